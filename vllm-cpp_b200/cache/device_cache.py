@@ -6,7 +6,9 @@ mixers keep, and owns the tensors:
 
 * a "kv" group -- all caches whose mixers keep keys and values of the same shape
   and the same window -- is one tensor
-  ``[caches in group, num_pages, 2 (K,V), kv_heads, page_size, head_dim]``: a page id
+  ``[caches in group, num_pages, 2 (K,V), kv_heads, page_size, head_dim]`` (where values
+  have another head size than keys: ``[caches, num_pages, kv_heads * page_size *
+  (head_dim + v_head_dim)]``, keys first): a page id
   means the same page in every cache of the group (as a page of the reference
   covers every layer, src/kv_cache_manager.cpp:15-29), head-major inside a page so
   the keys of one KV head are contiguous runs of page_size * head_dim;
@@ -39,7 +41,7 @@ class CacheGroup:
 @dataclass
 class KVCacheView:
     group: int               # index into the step context's groups
-    pages: torch.Tensor      # [num_pages, 2, kv_heads, page_size, head_dim] of one cache
+    pages: torch.Tensor      # [num_pages, 2, kv_heads, page_size, head_dim] of one cache (or [num_pages, row], see CacheSpec.v_head_dim)
 
 
 @dataclass
@@ -54,7 +56,7 @@ class CacheLayout:
     def __init__(self, cache_specs: dict[int, CacheSpec]):
         self.groups: list[CacheGroup] = []
         by_spec: dict[CacheSpec, CacheGroup] = {}
-        for cid in sorted(cache_specs):
+        for cid in sorted(cache_specs, key=lambda c: c if isinstance(c, tuple) else (c, -1)):
             spec = cache_specs[cid]
             if spec not in by_spec:
                 by_spec[spec] = CacheGroup(spec, [], paged=(spec.kind == "kv"))
@@ -76,11 +78,13 @@ class CacheLayout:
 
     def runtime_groups(self, runtime, page_size: int, num_pages: int):
         """GroupSpec list for the host CacheManager, one pool per paged group."""
-        return [runtime.GroupSpec(self.page_size_of(g, page_size), self.num_pages_of(g, page_size, num_pages), g.spec.window)
+        return [runtime.GroupSpec(self.page_size_of(g, page_size), self.num_pages_of(g, page_size, num_pages), g.spec.window,
+                                  g.spec.keep_first if g.spec.window else 0)
                 for g in self.paged]
 
     def bytes_per_token(self, elem_size: int) -> int:
-        return sum(len(g.cache_ids) * 2 * g.spec.num_kv_heads * g.spec.head_dim * elem_size for g in self.paged)
+        return sum(len(g.cache_ids) * g.spec.num_kv_heads * (g.spec.head_dim + (g.spec.v_head_dim or g.spec.head_dim)) * elem_size
+                   for g in self.paged)
 
 
 class DeviceCache:
@@ -91,8 +95,12 @@ class DeviceCache:
         for g in layout.groups:
             n = len(g.cache_ids)
             if g.paged:
-                shape = (n, layout.num_pages_of(g, page_size, num_pages), 2, g.spec.num_kv_heads,
-                         layout.page_size_of(g, page_size), g.spec.head_dim)
+                pages, ps = layout.num_pages_of(g, page_size, num_pages), layout.page_size_of(g, page_size)
+                if g.spec.v_head_dim and g.spec.v_head_dim != g.spec.head_dim:
+                    # values of another size than keys: a page is one flat row, keys first
+                    shape = (n, pages, g.spec.num_kv_heads * ps * (g.spec.head_dim + g.spec.v_head_dim))
+                else:
+                    shape = (n, pages, 2, g.spec.num_kv_heads, ps, g.spec.head_dim)
                 self.tensors.append(torch.zeros(shape, dtype=dtype, device=device))
             else:
                 sdt = _TORCH_DTYPES[g.spec.dtype]

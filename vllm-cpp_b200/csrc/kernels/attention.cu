@@ -9,6 +9,11 @@
 //   s_j = (q . k_j) / sqrt(head_dim),  j in (pos - window, pos],  softmax,  sum_j w_j v_j
 // as in the reference's compute_attention (src/model.cpp:1000-1052) and its paged
 // form (src/paged_attention.cpp:11-90), without the 1e-9 guard in the divisor.
+// Options for other designs, all off by default: the scale is an argument; with a
+// window, the first keep_first keys of a request stay visible to every later query
+// (at their true positions); a per-head penalty a_h * ln(1 + b_h * (pos - j)) is
+// taken off the score of key j; values may have another head size than keys (a page
+// is then [nkv][page_size][hd] keys followed by [nkv][page_size][hd_v] values).
 // Items whose key range is sliced write (max, sum, unnormalised output) partials,
 // merged by attn_merge_kernel in slice order.
 #include "common.cuh"
@@ -40,6 +45,11 @@ struct AttnArgs {
     // bounds of the partial-result buffers, for callers whose buffers have a fixed size (0: not checked): decoded
     // tokens and key slices that part_o / part_ml were laid out for
     int part_tokens, part_slices;
+    // the options: kept first keys, distance penalty per head (null: none), value head size
+    int keep_first;
+    const float* dist_a;
+    const float* dist_b;
+    int hd_v;
 };
 
 template <typename T> struct Vec8;
@@ -71,7 +81,9 @@ __global__ __launch_bounds__(TK) void attn_paged_kernel(AttnArgs a) {
     float* m_s = p_s + RMAX * TK;           // [RMAX] running maximum
     float* l_s = m_s + RMAX;                // [RMAX] running sum
     float* al_s = l_s + RMAX;               // [RMAX] rescale factor of the current tile
-    long long* voff_s = reinterpret_cast<long long*>(al_s + RMAX);  // [TK] element offset of each key's V row
+    float* da_s = al_s + RMAX;              // [RMAX] distance penalty of the row's head: a, b
+    float* db_s = da_s + RMAX;
+    long long* voff_s = reinterpret_cast<long long*>(db_s + RMAX);  // [TK] element offset of each key's V row
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int* item = a.items + (size_t)blockIdx.x * ITEM_INTS;
@@ -117,6 +129,12 @@ __global__ __launch_bounds__(TK) void attn_paged_kernel(AttnArgs a) {
     const int pps = (pb_hi - pb_lo + nslices - 1) / nslices;
     const int my_pb_lo = pb_lo + slice * pps, my_pb_hi = min(pb_hi, my_pb_lo + pps);
     const int k_begin = max(lo, my_pb_lo * ps), k_end = min(hi, my_pb_hi * ps);
+    // kept first keys that lie before the item's window: the first slice reads them ahead of its own range
+    const int KF = W > 0 ? a.keep_first : 0;
+    const int n_first = slice == 0 ? min(KF, lo) : 0;
+    const int n_keys = n_first + max(0, k_end - k_begin);
+    const int hdv = a.hd_v;
+    const bool vec_ok = (hd % 8) == 0;
 
     // queries -> shared memory, scaled
     const T* qg = reinterpret_cast<const T*>(a.q);
@@ -128,6 +146,9 @@ __global__ __launch_bounds__(TK) void attn_paged_kernel(AttnArgs a) {
     if (tid < RMAX) {
         m_s[tid] = -CUDART_INF_F;
         l_s[tid] = 0.f;
+        const int h = head0 + tid % gq;
+        da_s[tid] = a.dist_a != nullptr && tid < R ? a.dist_a[h] : 0.f;
+        db_s[tid] = a.dist_a != nullptr && tid < R ? a.dist_b[h] : 0.f;
     }
     constexpr int DPT = VCB_MAX_HEAD_DIM / TK;  // output dims per thread
     float acc_o[RMAX][DPT];
@@ -140,11 +161,12 @@ __global__ __launch_bounds__(TK) void attn_paged_kernel(AttnArgs a) {
     const T* pages = reinterpret_cast<const T*>(a.pages);
     const int* bt = a.block_table + (size_t)(a.table_row ? a.table_row[e] : e) * a.max_blocks;
 
-    for (int t0 = k_begin; t0 < k_end; t0 += TK) {
-        const int n_valid = min(TK, k_end - t0);
+    for (int u0 = 0; u0 < n_keys; u0 += TK) {
+        const int n_valid = min(TK, n_keys - u0);
         // ---- phase 1: one key per thread, scores of all rows ----
         {
-            const int kidx = t0 + tid;
+            const int u = u0 + tid;
+            const int kidx = u < n_first ? u : k_begin + (u - n_first);
             float s[RMAX];
 #pragma unroll
             for (int r = 0; r < RMAX; ++r) s[r] = 0.f;
@@ -156,10 +178,20 @@ __global__ __launch_bounds__(TK) void attn_paged_kernel(AttnArgs a) {
                     valid = false;
                     voff_s[tid] = -1;
                 } else {
-                    const long long base = (long long)page * a.page_stride + ((long long)kvh * ps + kidx % ps) * hd;
-                    voff_s[tid] = base + (long long)a.nkv * ps * hd;
+                    const long long in_page = (long long)kvh * ps + kidx % ps;
+                    const long long base = (long long)page * a.page_stride + in_page * hd;
+                    voff_s[tid] = (long long)page * a.page_stride + (long long)a.nkv * ps * hd + in_page * hdv;
                     const T* kp = pages + base;
-                    for (int c = 0; c < hd; c += 8) {
+                    if (!vec_ok) {
+                        // a head size that is no multiple of 8: element by element
+                        for (int c = 0; c < hd; ++c) {
+                            const float kf = to_f32(kp[c]);
+#pragma unroll
+                            for (int r = 0; r < RMAX; ++r)
+                                if (r < R) s[r] = fmaf(kf, q_s[r * hd + c], s[r]);
+                        }
+                    }
+                    for (int c = 0; vec_ok && c < hd; c += 8) {
                         float kf[8];
                         Vec8<T>::load(kp + c, kf);
 #pragma unroll
@@ -180,8 +212,10 @@ __global__ __launch_bounds__(TK) void attn_paged_kernel(AttnArgs a) {
             for (int r = 0; r < RMAX; ++r) {
                 if (r < R) {
                     const int pos = pos0 + r / gq;
-                    const bool seen = valid && kidx <= pos && (W <= 0 || kidx > pos - W);
-                    p_s[r * TK + tid] = seen ? s[r] : -CUDART_INF_F;
+                    const bool seen = valid && kidx <= pos && (W <= 0 || kidx > pos - W || kidx < KF);
+                    float sc = s[r];
+                    if (a.dist_a != nullptr && seen) sc -= da_s[r] * logf(1.f + db_s[r] * (float)(pos - kidx));
+                    p_s[r * TK + tid] = seen ? sc : -CUDART_INF_F;
                 }
             }
         }
@@ -218,7 +252,7 @@ __global__ __launch_bounds__(TK) void attn_paged_kernel(AttnArgs a) {
 #pragma unroll
         for (int i = 0; i < DPT; ++i) {
             const int d = tid + i * TK;
-            if (d < hd) {
+            if (d < hdv) {
 #pragma unroll
                 for (int r = 0; r < RMAX; ++r)
                     if (r < R) acc_o[r][i] *= al_s[r];
@@ -241,13 +275,13 @@ __global__ __launch_bounds__(TK) void attn_paged_kernel(AttnArgs a) {
 #pragma unroll
         for (int i = 0; i < DPT; ++i) {
             const int d = tid + i * TK;
-            if (d < hd) {
+            if (d < hdv) {
 #pragma unroll
                 for (int r = 0; r < RMAX; ++r) {
                     if (r < R) {
                         const float l = l_s[r];
                         const int iq = r / gq, ih = r % gq;
-                        og[((size_t)(row0 + iq) * a.nh + head0 + ih) * hd + d] = from_f32<T>(l > 0.f ? acc_o[r][i] / l : 0.f);
+                        og[((size_t)(row0 + iq) * a.nh + head0 + ih) * hdv + d] = from_f32<T>(l > 0.f ? acc_o[r][i] / l : 0.f);
                     }
                 }
             }
@@ -261,7 +295,7 @@ __global__ __launch_bounds__(TK) void attn_paged_kernel(AttnArgs a) {
 #pragma unroll
                 for (int i = 0; i < DPT; ++i) {
                     const int d = tid + i * TK;
-                    if (d < hd) a.part_o[prow * hd + d] = acc_o[r][i];
+                    if (d < hdv) a.part_o[prow * hdv + d] = acc_o[r][i];
                 }
                 if (tid == 0) {
                     a.part_ml[prow * 2] = m_s[r];
@@ -302,7 +336,7 @@ int launch_attn(const AttnArgs& a, int n_items, cudaStream_t stream) {
     const int g = a.nh / a.nkv;
     const int gq_max = g < RMAX ? g : RMAX;
     const int hchunks = (g + gq_max - 1) / gq_max;
-    const size_t smem = ((size_t)RMAX * a.hd + (size_t)RMAX * TK + 3 * RMAX) * sizeof(float) + TK * sizeof(long long);
+    const size_t smem = ((size_t)RMAX * a.hd + (size_t)RMAX * TK + 5 * RMAX) * sizeof(float) + TK * sizeof(long long);
     auto kern = attn_paged_kernel<T, RMAX>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -319,6 +353,30 @@ int launch_attn(const AttnArgs& a, int n_items, cudaStream_t stream) {
 }  // namespace
 
 // rows_max: 8 for items of single decoded tokens (key range may be sliced), 32 for prompt portions
+// keep_first, dist_a / dist_b (float [nh] each, or null) and hd_v (0: as hd): the options named at the top of this file.
+// With them the key head size may be any number up to the largest; values likewise.
+VCB_API int vcb_attn_paged_ex(const void* q, void* out, int dtype, const void* pages, long long page_stride,
+                              const int* block_table, const int* table_row, int max_blocks, const int* q_start, const int* q_len,
+                              const int* ctx_len, const int* items, int n_items, int rows_max, float* part_o,
+                              float* part_ml, int nh, int nkv, int hd, int page_size, int num_pages, int window,
+                              float scale, int keep_first, const float* dist_a, const float* dist_b, int hd_v, int* status,
+                              cudaStream_t stream) {
+    if (n_items == 0) return 0;
+    if (hd_v <= 0) hd_v = hd;
+    VCB_CHECK_ARG(nh > 0 && nkv > 0 && nh % nkv == 0, "attn_paged: %d query heads are not a multiple of %d KV heads", nh, nkv);
+    VCB_CHECK_ARG(hd >= 1 && hd <= VCB_MAX_HEAD_DIM && hd_v >= 1 && hd_v <= VCB_MAX_HEAD_DIM,
+                  "attn_paged: head sizes %d (keys) and %d (values) must lie in [1, %d]", hd, hd_v, VCB_MAX_HEAD_DIM);
+    VCB_CHECK_ARG(hd % 8 != 0 || (page_stride % 8 == 0 && ((long long)nkv * page_size * hd) % 8 == 0),
+                  "attn_paged: pages whose keys do not start on 8 elements (stride %lld)", page_stride);
+    VCB_CHECK_ARG(rows_max == 8 || rows_max == 32, "attn_paged: rows_max must be 8 or 32");
+    VCB_CHECK_ARG(page_size > 0 && window >= 0 && keep_first >= 0, "attn_paged: bad page_size %d, window %d or keep_first %d", page_size, window, keep_first);
+    VCB_CHECK_ARG((dist_a == nullptr) == (dist_b == nullptr), "attn_paged: the distance penalty needs both of its vectors");
+    AttnArgs a{q, out, pages, page_stride, block_table, table_row, max_blocks, q_start, q_len, ctx_len, items, part_o, part_ml,
+               nh, nkv, hd, page_size, num_pages, window, scale, status, 0, 0, keep_first, dist_a, dist_b, hd_v};
+    if (dtype == VCB_F32) return rows_max == 8 ? launch_attn<float, 8>(a, n_items, stream) : launch_attn<float, 32>(a, n_items, stream);
+    return rows_max == 8 ? launch_attn<__nv_bfloat16, 8>(a, n_items, stream) : launch_attn<__nv_bfloat16, 32>(a, n_items, stream);
+}
+
 VCB_API int vcb_attn_paged(const void* q, void* out, int dtype, const void* pages, long long page_stride,
                            const int* block_table, const int* table_row, int max_blocks, const int* q_start, const int* q_len,
                            const int* ctx_len, const int* items, int n_items, int rows_max, float* part_o,
@@ -330,7 +388,7 @@ VCB_API int vcb_attn_paged(const void* q, void* out, int dtype, const void* page
     VCB_CHECK_ARG(rows_max == 8 || rows_max == 32, "attn_paged: rows_max must be 8 or 32");
     VCB_CHECK_ARG(page_size > 0 && window >= 0, "attn_paged: bad page_size %d or window %d", page_size, window);
     AttnArgs a{q, out, pages, page_stride, block_table, table_row, max_blocks, q_start, q_len, ctx_len, items, part_o, part_ml,
-               nh, nkv, hd, page_size, num_pages, window, scale, status, 0, 0};
+               nh, nkv, hd, page_size, num_pages, window, scale, status, 0, 0, 0, nullptr, nullptr, hd};
     if (dtype == VCB_F32) return rows_max == 8 ? launch_attn<float, 8>(a, n_items, stream) : launch_attn<float, 32>(a, n_items, stream);
     return rows_max == 8 ? launch_attn<__nv_bfloat16, 8>(a, n_items, stream) : launch_attn<__nv_bfloat16, 32>(a, n_items, stream);
 }
@@ -420,7 +478,7 @@ VCB_API int vcb_attn_decode_no_alloc(const void* q, void* out, int dtype, const 
     // naming a token or slice beyond it, or another slice count, sets VCB_STATUS_BAD_ITEM and writes nothing.
     VCB_CHECK_ARG(status != nullptr, "attn_decode_no_alloc: a status word is required (bad items are reported there)");
     AttnArgs a{q, out, pages, page_stride, block_table, table_row, max_blocks, q_start, q_len, ctx_len, items, part_o,
-               part_ml, nh, nkv, hd, page_size, num_pages, window, scale, status, n_dec, nslices};
+               part_ml, nh, nkv, hd, page_size, num_pages, window, scale, status, n_dec, nslices, 0, nullptr, nullptr, hd};
     const int rc = dtype == VCB_F32 ? launch_attn<float, 8>(a, n_dec * nslices, stream)
                                     : launch_attn<__nv_bfloat16, 8>(a, n_dec * nslices, stream);
     if (rc) return rc;

@@ -1,0 +1,376 @@
+// Kernels of layers that mix a few neighbouring tokens per channel and gate what a sublayer returns:
+//
+//  * embed_sinusoid      x[t] = E[id_t] + s(p_t),  s(p)[2i] = sin(p f_i),  s(p)[2i+1] = cos(p f_i)
+//  * causal_conv         y_t = sum_j w[:, j] u_(t - taps + 1 + j)  per channel, u = 0 before a request's first token;
+//                        the taps - 1 inputs before a portion come from the request's state row
+//  * conv_state_update   the state row afterwards: the last taps - 1 inputs the request has seen
+//  * qkv_conv_norm_store the same convolution on the stacked q, k, v projection (with its bias), then every query
+//                        and key head divided by its root mean square, queries to a buffer, keys and values to
+//                        the tokens' cache slots
+//  * gated_norm_add      x_t += w * n(y_t * sigmoid(g_t + b)),  n(v) = v / sqrt(mean(v^2) + eps)
+//  * bias_act            act(u + b) for the feed-forward's hidden layer (erf or tanh GELU)
+//
+// All arithmetic is 32-bit; inputs that are matrix products arrive as 32-bit sums, possibly as k-slice partial sums
+// [S, T, C] that are added here in slice order.  A step's rows belong to entries (q_start, q_len per entry, rows in
+// entry order); rows beyond every entry (padding of a captured step) are left alone.
+#include "common.cuh"
+
+namespace {
+
+constexpr int MAX_TAPS = 8;
+
+// the entry a row belongs to, or -1: the last entry that starts at or before the row (entries without tokens share
+// their start with the one after them, so the last of equals is the one that has the row)
+__device__ __forceinline__ int entry_of_row(const int* __restrict__ q_start, const int* __restrict__ q_len, int E, int t) {
+    int lo = 0, hi = E;   // first index with q_start > t
+    while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (q_start[mid] <= t) lo = mid + 1;
+        else hi = mid;
+    }
+    const int e = lo - 1;
+    if (e < 0) return -1;
+    return t - q_start[e] < q_len[e] ? e : -1;
+}
+
+struct RowsIn {
+    const float* p;       // [S][T][ld] 32-bit sums
+    int S;
+    long long s_stride;   // elements between partial sums
+    long long ld;         // elements between rows
+    const float* bias;    // [C] or null
+};
+
+__device__ __forceinline__ float rows_at(const RowsIn& in, long long t, int c) {
+    float v = 0.f;
+    const float* p = in.p + t * in.ld + c;
+    for (int s = 0; s < in.S; ++s) v += p[(long long)s * in.s_stride];
+    if (in.bias != nullptr) v += in.bias[c];
+    return v;
+}
+
+// sum_j w[c][j] * u(rel - taps + 1 + j) for the row at place `rel` of its entry (row index t); places before the
+// entry's first row come from the state row st[k][c], k = place + taps - 1
+__device__ __forceinline__ float conv_at(const RowsIn& in, const float* __restrict__ w, const float* __restrict__ st, int C,
+                                         int taps, long long t, int rel, int c) {
+    float y = 0.f;
+    for (int j = 0; j < taps; ++j) {
+        const int back = taps - 1 - j;
+        const float u = rel - back >= 0 ? rows_at(in, t - back, c) : st[(long long)(rel + j) * C + c];
+        y = fmaf(w[(long long)c * taps + j], u, y);
+    }
+    return y;
+}
+
+__global__ void embed_sinusoid_kernel(const void* __restrict__ table, int table_dtype, const int* __restrict__ ids,
+                                      const int* __restrict__ positions, const float* __restrict__ inv_freq,
+                                      float* __restrict__ out, int H, int V, int* __restrict__ status) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x;
+    int id = ids[t];
+    if (id < 0 || id >= V) {
+        if (threadIdx.x == 0 && status != nullptr) atomicOr(status, VCB_STATUS_BAD_TOKEN);
+        id = 0;
+    }
+    const float p = (float)positions[t];
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        const float ang = p * inv_freq[c >> 1];
+        const float s = (c & 1) ? cosf(ang) : sinf(ang);
+        out[(size_t)t * H + c] = load_as_f32(table, table_dtype, (size_t)id * H + c) + s;
+    }
+}
+
+template <typename TOUT>
+__global__ void causal_conv_kernel(RowsIn in, const float* __restrict__ w, const float* __restrict__ state,
+                                   long long slot_stride, const int* __restrict__ q_start, const int* __restrict__ q_len,
+                                   const int* __restrict__ slots, int E, int T, int C, int taps, int add_input,
+                                   TOUT* __restrict__ out_conv, TOUT* __restrict__ out_copy) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.y;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const int e = entry_of_row(q_start, q_len, E, t);
+    if (e < 0) return;
+    const float u = rows_at(in, t, c);
+    if (out_copy != nullptr) out_copy[(size_t)t * C + c] = from_f32<TOUT>(u);
+    if (out_conv != nullptr) {
+        float y = taps > 0 ? conv_at(in, w, state + (long long)slots[e] * slot_stride, C, taps, t, t - q_start[e], c) : 0.f;
+        if (add_input) y += u;
+        out_conv[(size_t)t * C + c] = from_f32<TOUT>(y);
+    }
+}
+
+__global__ void conv_state_update_kernel(RowsIn in, float* __restrict__ state, long long slot_stride,
+                                         const int* __restrict__ q_start, const int* __restrict__ q_len,
+                                         const int* __restrict__ slots, int C, int taps) {
+    pdl_trigger();
+    pdl_wait();
+    const int e = blockIdx.y;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int n = q_len[e];
+    if (c >= C || n <= 0) return;
+    float* st = state + (long long)slots[e] * slot_stride;
+    const int keep = taps - 1;
+    float old[MAX_TAPS];
+#pragma unroll
+    for (int k = 0; k < MAX_TAPS; ++k) old[k] = k < keep ? st[(long long)k * C + c] : 0.f;
+    const long long row0 = q_start[e];
+#pragma unroll
+    for (int k = 0; k < MAX_TAPS; ++k) {
+        if (k < keep) {
+            const int rel = n - keep + k;   // place within the portion of the input that lands in row k
+            float v;
+            if (rel >= 0) v = rows_at(in, row0 + rel, c);
+            else {
+                // fewer new tokens than the state holds: the old rows move up (index n + k < keep)
+                v = 0.f;
+#pragma unroll
+                for (int m = 0; m < MAX_TAPS; ++m)
+                    if (m == n + k) v = old[m];
+            }
+            st[(long long)k * C + c] = v;
+        }
+    }
+}
+
+struct QkvArgs {
+    RowsIn in;
+    const float* w;       // [C][taps] or null when taps == 0
+    const float* state;
+    long long slot_stride;
+    const int* q_start;
+    const int* q_len;
+    const int* slots;
+    const int* slot_map;  // [T]: page * page_size + offset of the token's cache entry, -1: none
+    int E, C, taps;
+    int nh, nkv, hd, hd_v;
+    int use_norm;
+    float eps;
+    void* q_out;          // [T][nh * hd]
+    void* pages;
+    long long page_stride;
+    int page_size, num_pages;
+    int has_kv;
+    int* status;
+};
+
+// a block a row; its warps take the heads in turn (query heads, then key heads, then value heads)
+template <typename TOUT>
+__global__ __launch_bounds__(256) void qkv_conv_norm_store_kernel(QkvArgs a) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int e = entry_of_row(a.q_start, a.q_len, a.E, t);
+    if (e < 0) return;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const int rel = t - a.q_start[e];
+    const float* st = a.state != nullptr ? a.state + (long long)a.slots[e] * a.slot_stride : nullptr;
+    const int units = a.nh + (a.has_kv ? 2 * a.nkv : 0);
+    long long slot = -1;
+    if (a.has_kv) {
+        slot = a.slot_map[t];
+        if (slot >= (long long)a.num_pages * a.page_size) {
+            if (threadIdx.x == 0 && a.status != nullptr) atomicOr(a.status, VCB_STATUS_BAD_PAGE);
+            slot = -1;
+        }
+    }
+    TOUT* q_out = reinterpret_cast<TOUT*>(a.q_out);
+    TOUT* pages = reinterpret_cast<TOUT*>(a.pages);
+    constexpr int PER = VCB_MAX_HEAD_DIM / 32;
+    for (int u = warp; u < units; u += nwarps) {
+        int c0, n, kind;   // kind 0: query, 1: key, 2: value
+        if (u < a.nh) { kind = 0; n = a.hd; c0 = u * a.hd; }
+        else if (u < a.nh + a.nkv) { kind = 1; n = a.hd; c0 = a.nh * a.hd + (u - a.nh) * a.hd; }
+        else { kind = 2; n = a.hd_v; c0 = (a.nh + a.nkv) * a.hd + (u - a.nh - a.nkv) * a.hd_v; }
+        float y[PER];
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            const int d = lane + 32 * i;
+            y[i] = 0.f;
+            if (d < n) {
+                y[i] = a.taps > 0 ? conv_at(a.in, a.w, st, a.C, a.taps, t, rel, c0 + d) : rows_at(a.in, t, c0 + d);
+                ss = fmaf(y[i], y[i], ss);
+            }
+        }
+        float mul = 1.f;
+        if (kind != 2 && a.use_norm) {
+            ss = warp_sum(ss);
+            mul = 1.f / sqrtf(ss / (float)n + a.eps);
+        }
+        if (kind == 0) {
+#pragma unroll
+            for (int i = 0; i < PER; ++i) {
+                const int d = lane + 32 * i;
+                if (d < n) q_out[(size_t)t * a.nh * a.hd + c0 + d] = from_f32<TOUT>(y[i] * mul);
+            }
+        } else if (slot >= 0) {
+            const long long page = slot / a.page_size, off = slot % a.page_size;
+            const int kvh = kind == 1 ? u - a.nh : u - a.nh - a.nkv;
+            const long long base = page * a.page_stride +
+                                   (kind == 1 ? ((long long)kvh * a.page_size + off) * a.hd
+                                              : (long long)a.nkv * a.page_size * a.hd + ((long long)kvh * a.page_size + off) * a.hd_v);
+#pragma unroll
+            for (int i = 0; i < PER; ++i) {
+                const int d = lane + 32 * i;
+                if (d < n) pages[base + d] = from_f32<TOUT>(y[i] * mul);
+            }
+        }
+    }
+}
+
+// x_t += w * n(y_t * sigmoid(g_t + b)); a block a row, the gated values kept in shared memory between the two passes
+template <typename TOUT>
+__global__ void gated_norm_add_kernel(float* __restrict__ resid, RowsIn y, RowsIn g, const float* __restrict__ w, float eps,
+                                      const int* __restrict__ q_start, const int* __restrict__ q_len, int E, int H,
+                                      TOUT* __restrict__ out_cast) {
+    extern __shared__ float vals[];   // [H] then 33 floats for the block sum
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x;
+    if (entry_of_row(q_start, q_len, E, t) < 0) return;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        float v = rows_at(y, t, c);
+        if (g.p != nullptr) v *= 1.f / (1.f + expf(-rows_at(g, t, c)));
+        vals[c] = v;
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, vals + H);
+    const float mul = 1.f / sqrtf(ss / (float)H + eps);
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        const float x = resid[(size_t)t * H + c] + vals[c] * mul * w[c];
+        resid[(size_t)t * H + c] = x;
+        if (out_cast != nullptr) out_cast[(size_t)t * H + c] = from_f32<TOUT>(x);
+    }
+}
+
+template <typename TOUT>
+__global__ void bias_act_kernel(RowsIn in, TOUT* __restrict__ out, long long total, int C, int kind) {
+    pdl_trigger();
+    pdl_wait();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long t = i / C;
+        const int c = (int)(i % C);
+        const float z = rows_at(in, t, c);
+        float r;
+        if (kind == 0) r = 0.5f * z * (1.f + erff(z * 0.70710678118654752440f));
+        else if (kind == 1) r = 0.5f * z * (1.f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
+        else r = z / (1.f + expf(-z));
+        out[i] = from_f32<TOUT>(r);
+    }
+}
+
+}  // namespace
+
+VCB_API int vcb_embed_sinusoid(const void* table, int table_dtype, const int* ids, const int* positions,
+                               const float* inv_freq, float* out, int T, int H, int V, int* status, cudaStream_t stream) {
+    if (T == 0) return 0;
+    launch_pdl(embed_sinusoid_kernel, dim3(T), dim3(256), 0, stream, table, table_dtype, ids, positions, inv_freq, out, H, V, status);
+    VCB_CHECK_LAUNCH("embed_sinusoid");
+    return 0;
+}
+
+// in: [S][T][ld] 32-bit (+ bias); out_conv = conv(in) (+ in with add_input), out_copy = in, both [T][C] of out_dtype,
+// either may be null.  taps 0: no convolution (out_conv = in with add_input, else zeros).  state [slots][taps-1][C].
+VCB_API int vcb_causal_conv(const float* in, int S, long long s_stride, long long ld, const float* bias, const float* w,
+                            const float* state, long long slot_stride, const int* q_start, const int* q_len,
+                            const int* slots, int E, int T, int C, int taps, int add_input, void* out_conv,
+                            void* out_copy, int out_dtype, cudaStream_t stream) {
+    if (T == 0 || C == 0) return 0;
+    VCB_CHECK_ARG(taps >= 0 && taps <= MAX_TAPS, "causal_conv: %d taps (0 to %d)", taps, MAX_TAPS);
+    VCB_CHECK_ARG(taps < 2 || state != nullptr, "causal_conv: a convolution over %d tokens needs the requests' state", taps);
+    VCB_CHECK_ARG(T <= 65535, "causal_conv: %d rows in one step (at most 65535)", T);
+    RowsIn r{in, S < 1 ? 1 : S, s_stride, ld, bias};
+    const dim3 grid((C + 255) / 256, T), block(256);
+    if (out_dtype == VCB_F32)
+        launch_pdl(causal_conv_kernel<float>, grid, block, 0, stream, r, w, state, slot_stride, q_start, q_len, slots, E, T, C,
+                   taps, add_input, (float*)out_conv, (float*)out_copy);
+    else
+        launch_pdl(causal_conv_kernel<__nv_bfloat16>, grid, block, 0, stream, r, w, state, slot_stride, q_start, q_len, slots, E,
+                   T, C, taps, add_input, (__nv_bfloat16*)out_conv, (__nv_bfloat16*)out_copy);
+    VCB_CHECK_LAUNCH("causal_conv");
+    return 0;
+}
+
+VCB_API int vcb_conv_state_update(const float* in, int S, long long s_stride, long long ld, const float* bias, float* state,
+                                  long long slot_stride, const int* q_start, const int* q_len, const int* slots, int E,
+                                  int C, int taps, cudaStream_t stream) {
+    if (E == 0 || C == 0 || taps < 2) return 0;
+    VCB_CHECK_ARG(taps <= MAX_TAPS, "conv_state_update: %d taps (at most %d)", taps, MAX_TAPS);
+    VCB_CHECK_ARG(E <= 65535, "conv_state_update: %d entries in one step (at most 65535)", E);
+    RowsIn r{in, S < 1 ? 1 : S, s_stride, ld, bias};
+    launch_pdl(conv_state_update_kernel, dim3((C + 255) / 256, E), dim3(256), 0, stream, r, state, slot_stride, q_start, q_len,
+               slots, C, taps);
+    VCB_CHECK_LAUNCH("conv_state_update");
+    return 0;
+}
+
+VCB_API int vcb_qkv_conv_norm_store(const float* in, int S, long long s_stride, long long ld, const float* bias,
+                                    const float* w, const float* state, long long slot_stride, const int* q_start,
+                                    const int* q_len, const int* slots, const int* slot_map, int E, int T, int taps, int nh,
+                                    int nkv, int hd, int hd_v, int use_norm, float eps, void* q_out, void* pages,
+                                    long long page_stride, int page_size, int num_pages, int has_kv, int out_dtype,
+                                    int* status, cudaStream_t stream) {
+    if (T == 0) return 0;
+    VCB_CHECK_ARG(taps >= 0 && taps <= MAX_TAPS, "qkv_conv_norm_store: %d taps (0 to %d)", taps, MAX_TAPS);
+    VCB_CHECK_ARG(taps < 2 || state != nullptr, "qkv_conv_norm_store: a convolution over %d tokens needs the requests' state", taps);
+    VCB_CHECK_ARG(hd >= 1 && hd <= VCB_MAX_HEAD_DIM && hd_v >= 1 && hd_v <= VCB_MAX_HEAD_DIM,
+                  "qkv_conv_norm_store: head sizes %d and %d must lie in [1, %d]", hd, hd_v, VCB_MAX_HEAD_DIM);
+    QkvArgs a{};
+    a.in = RowsIn{in, S < 1 ? 1 : S, s_stride, ld, bias};
+    a.w = w; a.state = state; a.slot_stride = slot_stride;
+    a.q_start = q_start; a.q_len = q_len; a.slots = slots; a.slot_map = slot_map;
+    a.E = E; a.C = nh * hd + (has_kv ? nkv * (hd + hd_v) : 0); a.taps = taps;
+    a.nh = nh; a.nkv = nkv; a.hd = hd; a.hd_v = hd_v; a.use_norm = use_norm; a.eps = eps;
+    a.q_out = q_out; a.pages = pages; a.page_stride = page_stride; a.page_size = page_size; a.num_pages = num_pages;
+    a.has_kv = has_kv; a.status = status;
+    const int units = nh + (has_kv ? 2 * nkv : 0);
+    const int threads = 32 * (units < 8 ? units : 8);
+    if (out_dtype == VCB_F32) launch_pdl(qkv_conv_norm_store_kernel<float>, dim3(T), dim3(threads), 0, stream, a);
+    else launch_pdl(qkv_conv_norm_store_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, a);
+    VCB_CHECK_LAUNCH("qkv_conv_norm_store");
+    return 0;
+}
+
+// y: the sublayer's result [Sy][T][ldy]; g: the gate's sums [Sg][T][ldg] with bias gb, or null: no gate.
+// out_cast (or null): the updated rows once more, in out_dtype.
+VCB_API int vcb_gated_norm_add(float* resid, const float* y, int Sy, long long y_stride, long long ldy, const float* g, int Sg,
+                               long long g_stride, long long ldg, const float* gb, const float* w, float eps,
+                               const int* q_start, const int* q_len, int E, int T, int H, void* out_cast, int out_dtype,
+                               cudaStream_t stream) {
+    if (T == 0) return 0;
+    RowsIn ry{y, Sy < 1 ? 1 : Sy, y_stride, ldy, nullptr};
+    RowsIn rg{g, Sg < 1 ? 1 : Sg, g_stride, ldg, gb};
+    const size_t smem = ((size_t)H + 64) * sizeof(float);
+    const int threads = H >= 1024 ? 1024 : (H >= 512 ? 512 : 256);
+    if (out_dtype == VCB_F32) {
+        auto kern = gated_norm_add_kernel<float>;
+        if (smem > 48 * 1024) VCB_CHECK_ARG(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess,
+                                            "gated_norm_add: %zu bytes of shared memory refused", smem);
+        launch_pdl(kern, dim3(T), dim3(threads), smem, stream, resid, ry, rg, w, eps, q_start, q_len, E, H, (float*)out_cast);
+    } else {
+        auto kern = gated_norm_add_kernel<__nv_bfloat16>;
+        if (smem > 48 * 1024) VCB_CHECK_ARG(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess,
+                                            "gated_norm_add: %zu bytes of shared memory refused", smem);
+        launch_pdl(kern, dim3(T), dim3(threads), smem, stream, resid, ry, rg, w, eps, q_start, q_len, E, H, (__nv_bfloat16*)out_cast);
+    }
+    VCB_CHECK_LAUNCH("gated_norm_add");
+    return 0;
+}
+
+// kind 0: GELU with erf, 1: GELU with tanh, 2: SiLU
+VCB_API int vcb_bias_act(const float* in, int S, long long s_stride, long long ld, const float* bias, void* out, int out_dtype,
+                         int T, int C, int kind, cudaStream_t stream) {
+    if (T == 0 || C == 0) return 0;
+    VCB_CHECK_ARG(kind >= 0 && kind <= 2, "bias_act: unknown activation %d", kind);
+    RowsIn r{in, S < 1 ? 1 : S, s_stride, ld, bias};
+    const long long total = (long long)T * C;
+    const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    if (out_dtype == VCB_F32) launch_pdl(bias_act_kernel<float>, dim3(blocks), dim3(256), 0, stream, r, (float*)out, total, C, kind);
+    else launch_pdl(bias_act_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, r, (__nv_bfloat16*)out, total, C, kind);
+    VCB_CHECK_LAUNCH("bias_act");
+    return 0;
+}

@@ -13,17 +13,19 @@ PYBIND11_MODULE(_vcb_runtime, m) {
     py::register_exception<CacheError>(m, "CacheError", PyExc_RuntimeError);
 
     py::class_<GroupSpec>(m, "GroupSpec")
-        .def(py::init([](int32_t page_size, int32_t num_pages, int32_t window) {
+        .def(py::init([](int32_t page_size, int32_t num_pages, int32_t window, int32_t keep_first) {
                  GroupSpec g;
                  g.page_size = page_size;
                  g.num_pages = num_pages;
                  g.window = window;
+                 g.keep_first = keep_first;
                  return g;
              }),
-             py::arg("page_size"), py::arg("num_pages"), py::arg("window") = 0)
+             py::arg("page_size"), py::arg("num_pages"), py::arg("window") = 0, py::arg("keep_first") = 0)
         .def_readwrite("page_size", &GroupSpec::page_size)
         .def_readwrite("num_pages", &GroupSpec::num_pages)
-        .def_readwrite("window", &GroupSpec::window);
+        .def_readwrite("window", &GroupSpec::window)
+        .def_readwrite("keep_first", &GroupSpec::keep_first);
 
     py::class_<IdPool>(m, "IdPool")
         .def(py::init<int32_t>())

@@ -37,6 +37,7 @@ CacheManager::CacheManager(std::vector<GroupSpec> groups, int32_t num_slots)
     for (const auto& g : groups_) {
         if (g.page_size < 1) throw CacheError("page_size must be >= 1");
         if (g.window < 0) throw CacheError("window must be >= 0");
+        if (g.keep_first < 0) throw CacheError("keep_first must be >= 0");
         pools_.emplace_back(g.num_pages);
     }
 }
@@ -77,8 +78,9 @@ int32_t CacheManager::peak_pages(int32_t group, int32_t total_len, int32_t porti
     const GroupSpec& g = groups_.at(group);
     const int32_t all = ceil_div(total_len, g.page_size);
     if (g.window == 0) return all;
-    // a window group holds at most the window, one portion being written and a page of slack at each end
-    return std::min(all, ceil_div(g.window + std::max(portion, 1), g.page_size) + 1);
+    // a window group holds at most the window, one portion being written and a page of slack at each end,
+    // beside the pages of the first positions that it keeps for good
+    return std::min(all, ceil_div(g.window + std::max(portion, 1), g.page_size) + 1 + ceil_div(g.keep_first, g.page_size));
 }
 
 bool CacheManager::reserve(int64_t request, int32_t new_len) {
@@ -105,7 +107,8 @@ void CacheManager::commit(int64_t request, int32_t new_len) {
         // the next query sits at position new_len and reads keys >= new_len - W + 1
         const int32_t first_needed = std::max(0, new_len - spec.window + 1);
         const int32_t dead_blocks = std::min<int32_t>(first_needed / spec.page_size, (int32_t)q.tables[g].size());
-        for (int32_t b = 0; b < dead_blocks; ++b) {
+        // the pages of the kept first positions stay
+        for (int32_t b = ceil_div(spec.keep_first, spec.page_size); b < dead_blocks; ++b) {
             int32_t& page = q.tables[g][b];
             if (page >= 0) {
                 pools_[g].free(page);

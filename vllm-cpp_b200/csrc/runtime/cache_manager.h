@@ -46,6 +46,7 @@ struct GroupSpec {
     int32_t page_size = 16;  // tokens per page
     int32_t num_pages = 0;   // pages in this group's pool
     int32_t window = 0;      // 0: every key stays; W > 0: position p reads keys (p - W, p]
+    int32_t keep_first = 0;  // with a window: positions [0, keep_first) stay readable for good, so their pages are kept
 };
 
 class CacheManager {

@@ -7,6 +7,7 @@ from ..config.base import load_config_dict
 from ..parts import BuildContext  # registers the parts
 from ..registry import architecture_of, get_architecture
 from . import qwen3  # registers Qwen3ForCausalLM
+from . import rimopel  # registers Rimopel
 from .decoder import DecoderModel
 
 

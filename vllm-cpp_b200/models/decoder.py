@@ -37,6 +37,7 @@ class DecoderModel:
         self.lm_head = part_class("head", head.kind)(head.params, "", build)
         self.lm_head.attach(self.embedding)
         self.order = list(spec.order)
+        self._handed = None     # (the per-id views last given to forward, the same by run)
         for run in self.order:
             if not 0 <= run.layer < len(self.layers):
                 raise ValueError(f"the execution order names layer {run.layer}, the model has {len(self.layers)}")
@@ -66,13 +67,13 @@ class DecoderModel:
         self.lm_head.bind(store)
 
     # ---- caches ----
-    def cache_specs(self) -> dict[int, CacheSpec]:
-        """cache id -> what the writing run's mixer keeps there."""
-        specs: dict[int, CacheSpec] = {}
+    def _run_specs(self) -> dict[int, object]:
+        """cache id of the execution order -> what the writing run's layer keeps there (one spec or a tuple)."""
+        specs: dict[int, object] = {}
         for run in self.order:
             if run.cache is None or not run.writes:
                 continue
-            spec = self.layers[run.layer].mixer.cache_spec()
+            spec = self.layers[run.layer].cache_spec()
             if spec is None:
                 raise ValueError(f"layer {run.layer} was given cache {run.cache} but its mixer keeps nothing")
             if run.cache in specs:
@@ -82,17 +83,40 @@ class DecoderModel:
             if run.cache is not None and not run.writes:
                 if run.cache not in specs:
                     raise ValueError(f"layer {run.layer} reads cache {run.cache}, which no run writes")
-                if self.layers[run.layer].mixer.cache_spec() != specs[run.cache]:
+                if self.layers[run.layer].cache_spec() != specs[run.cache]:
                     raise ValueError(f"layer {run.layer} reads cache {run.cache} of another shape than it expects")
         return specs
+
+    def cache_specs(self) -> dict:
+        """cache id -> :class:`CacheSpec`.  A run whose layer keeps several things (a tuple of specs: pages of keys
+        and values beside a fixed-size state, say) has one id per thing, ``(run's cache id, index)``."""
+        specs: dict = {}
+        for cid, spec in self._run_specs().items():
+            if isinstance(spec, tuple):
+                for k, s in enumerate(spec):
+                    specs[(cid, k)] = s
+            else:
+                specs[cid] = spec
+        return specs
+
+    def run_caches(self, views: dict) -> dict:
+        """cache id of the execution order -> the view (or tuple of views) its runs are handed, from the per-id views."""
+        return {cid: (tuple(views[(cid, k)] for k in range(len(spec))) if isinstance(spec, tuple) else views[cid])
+                for cid, spec in self._run_specs().items()}
 
     # ---- one step ----
     def forward(self, ctx, caches):
         """ctx: the step's tensors; caches: cache id -> view.  Returns 32-bit logits [rows, vocab]."""
         mark = getattr(ctx, "mark", lambda label: None)     # kernel groups for the profile, where the step keeps one
-        resid = self.embedding.forward(ctx.token_ids, ctx.T, ctx.status)
+        if getattr(self.embedding, "uses_positions", False):
+            resid = self.embedding.forward(ctx.token_ids, ctx.T, ctx.status, positions=ctx.positions)
+        else:
+            resid = self.embedding.forward(ctx.token_ids, ctx.T, ctx.status)
         mark("embedding")
         pending = None
+        if self._handed is None or self._handed[0] is not caches:
+            self._handed = (caches, self.run_caches(caches))
+        caches = self._handed[1]
         for i, run in enumerate(self.order):
             cache = caches[run.cache] if run.cache is not None else None
             workspace.begin_run(i)      # the run's buffers come from the scratch region that run i - 2 used

@@ -69,6 +69,13 @@ def _declare(L):
         "vcb_sgemm_tn": [P, P, P, I, I, I, LL, LL, LL, P],
         "vcb_gemm_bf16_plain": [P, P, P, I, I, I, I, LL, LL, LL, P],
         "vcb_attn_paged": [P, P, I, P, LL, P, P, I, P, P, P, P, I, I, P, P, I, I, I, I, I, I, F, P, P],
+        "vcb_attn_paged_ex": [P, P, I, P, LL, P, P, I, P, P, P, P, I, I, P, P, I, I, I, I, I, I, F, I, P, P, I, P, P],
+        "vcb_embed_sinusoid": [P, I, P, P, P, P, I, I, I, P, P],
+        "vcb_causal_conv": [P, I, LL, LL, P, P, P, LL, P, P, P, I, I, I, I, I, P, P, I, P],
+        "vcb_conv_state_update": [P, I, LL, LL, P, P, LL, P, P, P, I, I, I, P],
+        "vcb_qkv_conv_norm_store": [P, I, LL, LL, P, P, P, LL, P, P, P, P, I, I, I, I, I, I, I, I, F, P, P, LL, I, I, I, I, P, P],
+        "vcb_gated_norm_add": [P, P, I, LL, LL, P, I, LL, LL, P, P, F, P, P, I, I, I, P, I, P],
+        "vcb_bias_act": [P, I, LL, LL, P, P, I, I, I, I, P],
         "vcb_scatter_i32": [P, P, P, P, I, LL, P],
         "vcb_selftest_wait_timeout": [LL, P, P, P],
         "vcb_state_reset": [P, I, LL, LL, LL, I, I, P, P, P, I, ctypes.c_uint, P, P],
@@ -371,6 +378,150 @@ def attn_paged(q, out, pages, block_table, q_start, q_len, ctx_len, items, n_ite
     _call("vcb_attn_paged", _p(q), _p(out), _dt(q), _p(pages), pages.stride(0), _p(block_table), _p(table_row), block_table.shape[1],
           _p(q_start), _p(q_len), _p(ctx_len), _p(items), n_items, rows_max, _p(part_o), _p(part_ml), nh, nkv, hd,
           page_size, num_pages, int(window or 0), 1.0 / math.sqrt(hd), _p(status), _stream())
+
+
+def kv_page_views(pages, nkv, hd, hd_v):
+    """(page_size, num_pages) of one cache's pages, laid out either [pages, 2, nkv, page_size, hd] or, where values
+    have another head size than keys, [pages, nkv * page_size * (hd + hd_v)]: keys first, then values."""
+    if pages.dim() == 5:
+        num_pages, two, nkv_p, page_size, hd_p = pages.shape
+        assert two == 2 and nkv_p == nkv and hd_p == hd == hd_v, (pages.shape, nkv, hd, hd_v)
+        return page_size, num_pages
+    assert pages.dim() == 2 and pages.shape[1] % (nkv * (hd + hd_v)) == 0, (pages.shape, nkv, hd, hd_v)
+    return pages.shape[1] // (nkv * (hd + hd_v)), pages.shape[0]
+
+
+def attn_window_bias(q, out, pages, block_table, q_start, q_len, ctx_len, items, n_items, rows_max, part_o, part_ml,
+                     nh, nkv, hd, window, status, table_row=None, *, scale, keep_first=0, dist_a=None, dist_b=None, hd_v=None):
+    """:func:`attn_paged` with its options: scores scaled by ``scale``; with a window, the first ``keep_first`` keys of
+    a request stay visible; ``dist_a``/``dist_b`` (float32 [nh]): a_h ln(1 + b_h (pos - j)) is taken off key j's
+    score; values of head size ``hd_v`` (``pages`` then [num_pages, nkv * page_size * (hd + hd_v)])."""
+    hd_v = hd if hd_v is None else int(hd_v)
+    _need(q, "q"); _need(out, "out", q.dtype); _need(pages, "pages", q.dtype)
+    for name, t in (("block_table", block_table), ("q_start", q_start), ("q_len", q_len), ("ctx_len", ctx_len),
+                    ("items", items)):
+        _need(t, name, torch.int32)
+    page_size, num_pages = kv_page_views(pages, nkv, hd, hd_v)
+    if dist_a is not None:
+        _need(dist_a, "dist_a", torch.float32); _need(dist_b, "dist_b", torch.float32)
+        assert dist_a.numel() == nh and dist_b.numel() == nh
+    _call("vcb_attn_paged_ex", _p(q), _p(out), _dt(q), _p(pages), pages.stride(0), _p(block_table), _p(table_row),
+          block_table.shape[1], _p(q_start), _p(q_len), _p(ctx_len), _p(items), n_items, rows_max, _p(part_o), _p(part_ml),
+          nh, nkv, hd, page_size, num_pages, int(window or 0), float(scale), int(keep_first or 0), _p(dist_a), _p(dist_b),
+          hd_v, _p(status), _stream())
+
+
+def embed_sinusoid(table, ids, positions, inv_freq, out, status):
+    """out[t] = table[ids[t]] + s(positions[t]) with s(p)[2i] = sin(p * inv_freq[i]), s(p)[2i+1] = cos(p * inv_freq[i])."""
+    _need(table, "table"); _need(ids, "ids", torch.int32); _need(positions, "positions", torch.int32)
+    _need(inv_freq, "inv_freq", torch.float32); _need(out, "out", torch.float32)
+    T, H = out.shape
+    assert table.shape[1] == H and ids.numel() >= T and positions.numel() >= T and inv_freq.numel() >= (H + 1) // 2
+    _call("vcb_embed_sinusoid", _p(table), _dt(table), _p(ids), _p(positions), _p(inv_freq), _p(out), T, H, table.shape[0],
+          _p(status), _stream())
+
+
+def _rows_in(t: torch.Tensor, name: str):
+    """A 32-bit [T, C] or [S, T, C] operand (rows may be strided) -> (S, stride between partial sums, row stride)."""
+    _need(t, name, torch.float32, contiguous=False)
+    assert t.stride(-1) == 1
+    if t.dim() == 2:
+        return 1, 0, t.stride(0)
+    return t.shape[0], t.stride(0), t.stride(1)
+
+
+def causal_conv(x, weight, state, q_start, q_len, slots, n_entries, out_conv=None, out_copy=None, bias=None,
+                add_input=False):
+    """Per channel, over the tokens of each entry: out_conv[t] = sum_j weight[:, j] x[t - taps + 1 + j] (+ x[t] with
+    ``add_input``), the taps - 1 inputs before an entry's first row read from ``state`` [slots, taps - 1, C] (32-bit)
+    at the entry's slot; out_copy[t] = x[t].  x: 32-bit [T, C] or [S, T, C] partial sums, ``bias`` [C] added.
+    ``weight`` None: no convolution.  Rows outside every entry are left alone."""
+    S, ss, ld = _rows_in(x, "x")
+    T, C = x.shape[-2:]
+    taps = 0 if weight is None else weight.shape[1]
+    if weight is not None:
+        _need(weight, "weight", torch.float32); assert weight.shape[0] == C
+    if taps > 1:
+        _need(state, "state", torch.float32); assert state.shape[1:] == (taps - 1, C), (state.shape, taps, C)
+    dt = None
+    for o in (out_conv, out_copy):
+        if o is not None:
+            _need(o, "out"); assert o.shape == (T, C); dt = _dt(o)
+    assert dt is not None
+    _call("vcb_causal_conv", _p(x), S, ss, ld, _p(bias), _p(weight), _p(state) if taps > 1 else None,
+          state.stride(0) if taps > 1 else 0, _p(q_start), _p(q_len), _p(slots), n_entries, T, C, taps, int(bool(add_input)),
+          _p(out_conv), _p(out_copy), dt, _stream())
+
+
+def conv_state_update(x, state, q_start, q_len, slots, n_entries, bias=None):
+    """After :func:`causal_conv` (or :func:`qkv_conv_norm_store`): each entry's state row holds the last taps - 1
+    inputs its request has seen (older ones move up where the entry brought fewer)."""
+    S, ss, ld = _rows_in(x, "x")
+    C = x.shape[-1]
+    _need(state, "state", torch.float32)
+    taps = state.shape[1] + 1
+    assert state.shape[2] == C
+    _call("vcb_conv_state_update", _p(x), S, ss, ld, _p(bias), _p(state), state.stride(0), _p(q_start), _p(q_len), _p(slots),
+          n_entries, C, taps, _stream())
+
+
+def qkv_conv_norm_store(qkv, bias, weight, state, q_start, q_len, slots, slot_map, n_entries, q_out, pages, nh, nkv, hd,
+                        hd_v, eps, status, use_norm=True, has_kv=True):
+    """The stacked q, k, v projection ``qkv`` (32-bit [T, C] or [S, T, C], C = nh hd + nkv (hd + hd_v)) with ``bias``
+    [C]; a causal convolution per channel (``weight`` [C, taps] or None) whose earlier inputs come from ``state``;
+    every query and key head divided by its root mean square (``eps`` inside the root); queries to ``q_out``
+    [T, nh hd], keys and values to the tokens' slots of ``pages`` (see :func:`kv_page_views`)."""
+    S, ss, ld = _rows_in(qkv, "qkv")
+    T, C = qkv.shape[-2:]
+    assert C == nh * hd + (nkv * (hd + hd_v) if has_kv else 0), (C, nh, nkv, hd, hd_v)
+    taps = 0 if weight is None else weight.shape[1]
+    if weight is not None:
+        _need(weight, "weight", torch.float32); assert weight.shape[0] == C
+    if taps > 1:
+        _need(state, "state", torch.float32); assert state.shape[1:] == (taps - 1, C)
+    _need(q_out, "q_out"); assert q_out.shape == (T, nh * hd)
+    page_size = num_pages = page_stride = 0
+    if has_kv:
+        _need(pages, "pages", q_out.dtype); _need(slot_map, "slot_map", torch.int32)
+        page_size, num_pages = kv_page_views(pages, nkv, hd, hd_v)
+        page_stride = pages.stride(0)
+    _call("vcb_qkv_conv_norm_store", _p(qkv), S, ss, ld, _p(bias), _p(weight), _p(state) if taps > 1 else None,
+          state.stride(0) if taps > 1 else 0, _p(q_start), _p(q_len), _p(slots), _p(slot_map), n_entries, T, taps, nh, nkv, hd,
+          hd_v, int(bool(use_norm)), float(eps), _p(q_out), _p(pages) if has_kv else None, page_stride, max(page_size, 1),
+          num_pages, int(bool(has_kv)), _dt(q_out), _p(status), _stream())
+
+
+def gated_norm_add(resid, y, gate, gate_bias, weight, eps, q_start, q_len, n_entries, out_cast=None):
+    """resid[t] += weight * n(y[t] * sigmoid(gate[t] + gate_bias)), n(v) = v / sqrt(mean(v^2) + eps); ``gate`` None: no
+    gate.  y, gate: 32-bit [T, H] or [S, T, H] partial sums (rows may be strided).  ``out_cast``: the new rows once more."""
+    _need(resid, "resid", torch.float32); _need(weight, "weight", torch.float32)
+    T, H = resid.shape
+    Sy, ssy, ldy = _rows_in(y, "y")
+    assert y.shape[-1] == H and y.shape[-2] >= T
+    Sg = ssg = ldg = 0
+    if gate is not None:
+        Sg, ssg, ldg = _rows_in(gate, "gate")
+        assert gate.shape[-1] == H and gate.shape[-2] >= T
+        if gate_bias is not None:
+            _need(gate_bias, "gate_bias", torch.float32)
+    if out_cast is not None:
+        _need(out_cast, "out_cast"); assert out_cast.shape == (T, H)
+    _call("vcb_gated_norm_add", _p(resid), _p(y), Sy, ssy, ldy, _p(gate), Sg, ssg, ldg, _p(gate_bias) if gate is not None else None,
+          _p(weight), float(eps), _p(q_start), _p(q_len), n_entries, T, H, _p(out_cast), _dt(out_cast) if out_cast is not None else F32,
+          _stream())
+
+
+ACTIVATIONS = {"gelu": 0, "gelu_erf": 0, "gelu_tanh": 1, "silu": 2}
+
+
+def bias_act(x, out, kind: str, bias=None):
+    """out = act(x + bias): x 32-bit [T, C] or [S, T, C] partial sums; ``kind`` one of ACTIVATIONS."""
+    S, ss, ld = _rows_in(x, "x")
+    T, C = x.shape[-2:]
+    _need(out, "out"); assert out.shape == (T, C)
+    if kind not in ACTIVATIONS:
+        raise KernelError(f"activation '{kind}' is not one of {sorted(ACTIVATIONS)}")
+    _call("vcb_bias_act", _p(x), S, ss, ld, _p(bias), _p(out), _dt(out), T, C, ACTIVATIONS[kind], _stream())
 
 
 def attn_merge(part_o, part_ml, dec_rows, out, n_dec, nh, hd, nslices):

@@ -78,10 +78,11 @@ class AttentionPlan:
     """Work items of the attention kernel for one step and one head layout, on the device."""
 
     def __init__(self, ctx, nh: int, nkv: int, decode_rows: int = DECODE_ROWS, span_rows: int = SPAN_ROWS,
-                 cluster_hd: int | None = None, one_slice: bool = False):
+                 cluster_hd: int | None = None, one_slice: bool = False, max_keys: int = 0):
         """``cluster_hd``: the head size, when the kernel that takes the decoded tokens can merge a token's key slices
         within a cluster of its blocks (then the slices are chosen so that all clusters run at once); else None.
-        ``one_slice``: no key slices, whatever the contexts."""
+        ``one_slice``: no key slices, whatever the contexts.  ``max_keys`` > 0: no query reads more keys than this
+        (a window), so the key ranges are sliced as if no context were longer."""
         g = nh // nkv
         dev = ctx.device
         # int32 arrays go to the device with the step's own staging buffers where the step has them
@@ -101,9 +102,13 @@ class AttentionPlan:
             if getattr(ctx, "static", False):
                 # a captured step serves every context length up to the bound it was captured for (None: any)
                 longest = getattr(ctx, "static_max_ctx", None)
+                if max_keys:
+                    longest = max_keys if longest is None else min(longest, max_keys)
                 by_pages = MAX_SLICES if longest is None else max(1, longest // 128)
             else:
                 longest = self.longest = max(ctx.host_ctx_len[i] for i in dec)
+                if max_keys:
+                    longest = min(longest, max_keys)
                 by_pages = max(1, longest // 128)   # at least 128 keys a slice
             # as many slices as keep every block resident in one wave; over short contexts no more than
             # SHORT_SLICES, beyond which merging the partial results costs more than the shorter key ranges save

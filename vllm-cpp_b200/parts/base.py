@@ -12,9 +12,10 @@ Families and what each must offer (beside ``tensor_specs`` and ``bind``):
                   residual stream, returns the normalised rows in the activation
                   dtype; with ``rows`` only those rows, and the stream is left alone.
 ``position``      whatever its mixer asks of it (the rotary part: a ``table``).
-``mixer``         ``cache_spec()`` -> what it keeps per request (a :class:`CacheSpec`
-                  or ``None``); ``forward(x, ctx, cache, writes) -> delta`` where
-                  ``cache`` is the view of the cache this run was given.
+``mixer``         ``cache_spec()`` -> what it keeps per request (a :class:`CacheSpec`,
+                  a tuple of them, or ``None``); ``forward(x, ctx, cache, writes) ->
+                  delta`` where ``cache`` is the view of the cache this run was given
+                  (a tuple of views for a tuple of specs, in the same order).
 ``feed_forward``  ``forward(x, ctx) -> delta``.
 ``block``         the arrangement: ``forward(resid, pending, ctx, cache, writes) ->
                   pending`` where ``pending`` is a delta not yet added to ``resid``.
@@ -49,7 +50,12 @@ class CacheSpec:
                   token, in pages; ``window`` > 0 means only the last ``window``
                   keys are ever read, so older pages may be given back;
                   ``page_size`` > 0 asks for pages of that many tokens instead of
-                  the engine's (caches that differ in it get pools of their own).
+                  the engine's (caches that differ in it get pools of their own);
+                  with a window, ``keep_first`` > 0 keeps the request's first keys
+                  readable for good, so the pages that hold them are never given back;
+                  ``v_head_dim`` > 0: values of another size than keys (a page then
+                  holds ``[num_kv_heads, page_size, head_dim]`` keys followed by
+                  ``[num_kv_heads, page_size, v_head_dim]`` values, as one flat row).
     kind "state": a block of fixed size per request, ``shape`` of ``dtype``,
                   addressed by the request's slot."""
     kind: str
@@ -60,6 +66,8 @@ class CacheSpec:
     dtype: str = "float32"
     page_size: int = 0
     initial_value: float = 0.0    # kind "state": what a request's state holds before its first token
+    keep_first: int = 0
+    v_head_dim: int = 0
 
 
 class Part:
@@ -125,6 +133,11 @@ class Block(Part):
     @property
     def mixer(self) -> Mixer:
         return self.parts["mixer"]
+
+    def cache_spec(self):
+        """What a run of this layer keeps per request: the mixer's needs, unless the arrangement has some of its own
+        (it then returns a tuple and takes the views apart in ``forward``)."""
+        return self.mixer.cache_spec()
 
     def forward(self, resid, pending, ctx, cache, writes: bool = True):
         raise NotImplementedError

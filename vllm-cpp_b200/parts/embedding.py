@@ -59,6 +59,31 @@ class TokenEmbedding(Embedding):
         return out
 
 
+class SinusoidalTokenEmbedding(TokenEmbedding):
+    """x[t] = E[id_t] + s(p_t): a sinusoid of the token's position is added to its embedding, entry 2i of s(p) being
+    sin(p * base^(-2i/hidden)) and entry 2i+1 the cosine of the same angle.  The frequencies are computed in 64-bit
+    on the host and rounded once; angles, sines and cosines are 32-bit on the device, so no table bounds the positions.
+
+    params: ``tensor``, ``vocab_size``, ``hidden_size``, ``base`` (default 10000)."""
+    uses_positions = True      # the model hands forward the tokens' positions too
+
+    def __init__(self, params, prefix, build):
+        super().__init__(params, prefix, build)
+        self.base = float(params.get("base", 10000.0))
+        key = ("sinusoid_freq", self.hidden, self.base)
+        if key not in build.shared:
+            i = torch.arange((self.hidden + 1) // 2, dtype=torch.float64)
+            build.shared[key] = (self.base ** (-2.0 * i / self.hidden)).to(torch.float32).to(build.device)
+        self.inv_freq = build.shared[key]
+
+    def forward(self, ids, n_tokens, status, positions=None):
+        if positions is None:
+            raise ValueError("this embedding adds a position term: it needs the tokens' positions")
+        out = workspace.empty((n_tokens, self.hidden), torch.float32, ids.device)
+        ops.embed_sinusoid(self.table, ids, positions, self.inv_freq, out, status)
+        return out
+
+
 class LMHead(Head):
     """params: ``tensor`` (checkpoint name of the head matrix, or None: the embedding table is the head),
     ``vocab_size``, ``hidden_size``."""

@@ -56,3 +56,36 @@ class SwiGLUMLP(FeedForward):
             ops.swiglu(gate_up, act)
             return matmul_tn(act, self.w_down, ctx.status, out_dtype=torch.float32, allow_partials=True, after_small_kernel=True)
         return matmul_tn(act, self.w_down, ctx.status, out_dtype=torch.float32, allow_partials=True)
+
+
+class DenseMLP(FeedForward):
+    """down(act(up(y))): one hidden layer, act the exact (erf) GELU unless ``activation`` names another
+    ("gelu_erf", "gelu_tanh": 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))), "silu").  The hidden layer's sums and
+    the activation are 32-bit; what the down projection reads is in the compute dtype.
+
+    params: ``hidden_size``, ``intermediate_size``; optional ``activation``, ``up_tensor`` and ``down_tensor``
+    (names under the prefix, default "up_proj.weight" and "down_proj.weight")."""
+
+    def __init__(self, params, prefix, build):
+        super().__init__(params, prefix, build)
+        self.hidden = int(params["hidden_size"])
+        self.inter = int(params["intermediate_size"])
+        self.activation = str(params.get("activation", "gelu_erf"))
+        if self.activation not in ops.ACTIVATIONS:
+            raise ValueError(f"activation '{self.activation}' is not one of {sorted(ops.ACTIVATIONS)}")
+        self.up_name = prefix + str(params.get("up_tensor", "up_proj.weight"))
+        self.down_name = prefix + str(params.get("down_tensor", "down_proj.weight"))
+        self.w_up = self.w_down = None
+
+    def tensor_specs(self):
+        return [TensorSpec(self.up_name, (self.inter, self.hidden)), TensorSpec(self.down_name, (self.hidden, self.inter))]
+
+    def bind(self, store):
+        self.w_up = store.matrix(self.up_name)
+        self.w_down = store.matrix(self.down_name)
+
+    def forward(self, x, ctx):
+        u = matmul_tn(x, self.w_up, ctx.status, out_dtype=torch.float32, allow_partials=True)
+        act = workspace.empty((x.shape[0], self.inter), x.dtype, x.device)
+        ops.bias_act(u, act, self.activation)
+        return matmul_tn(act, self.w_down, ctx.status, out_dtype=torch.float32, allow_partials=True, after_small_kernel=True)

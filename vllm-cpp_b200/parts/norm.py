@@ -11,19 +11,20 @@ from .base import Norm
 
 
 class RMSNorm(Norm):
-    """params: ``size``, ``eps``.  Tensor: ``<prefix>weight`` [size]."""
+    """params: ``size``, ``eps``; optional ``name`` (default "weight").  Tensor: ``<prefix><name>`` [size]."""
 
     def __init__(self, params, prefix, build):
         super().__init__(params, prefix, build)
         self.size = int(params["size"])
         self.eps = float(params["eps"])
+        self.name = self.prefix + str(params.get("name", "weight"))
         self.weight = None
 
     def tensor_specs(self):
-        return [TensorSpec(self.prefix + "weight", (self.size,), "vector")]
+        return [TensorSpec(self.name, (self.size,), "vector")]
 
     def bind(self, store):
-        self.weight = store.vector(self.prefix + "weight")
+        self.weight = store.vector(self.name)
 
     def forward(self, resid, delta, rows=None):
         n = resid.shape[0] if rows is None else rows.numel()

@@ -1,0 +1,123 @@
+"""Grouped-query attention without rotation, for designs that tell positions apart by distance:
+
+    u = W [q; k; v] x + b                         (one stacked product)
+    u'_t = sum_j c[:, j] u_(t - taps + 1 + j)     a short causal convolution per channel, zero before the first token
+    q, k  <-  each head divided by its root mean square over the head (no gain; eps inside the root)
+    s_ij = scale * (q_i . k_j) - a_h ln(1 + b_h (i - j))
+    i sees j  iff  j <= i and (i - j < window or j < keep_first)
+    softmax over the visible keys, weighted sum of the values, output projection.
+
+Query head h reads key/value head h // (heads / kv_heads); keys have ``head_dim`` lanes, values ``v_head_dim``.  The
+first ``keep_first`` keys of a request stay visible at their true distances.  Every option can be switched off (no
+bias, no convolution, no norm, no penalty, no window), so the part serves other designs of this family.
+
+Per request the part keeps the keys and values in pages (given back as the window passes, except the pages of the
+kept first keys) and, for the convolution, the last taps - 1 rows of the stacked projection as a fixed-size state.
+Scores, softmax, the penalty, the norms and the convolution are 32-bit; keys, values and queries are stored in the
+compute dtype.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import ops, workspace
+from ..weights.loader import TensorSpec
+from .attention import DECODE_ROWS, SPAN_ROWS, AttentionPlan
+from .base import CacheSpec, Mixer
+from .linear import matmul_tn
+
+
+class ConvWindowAttention(Mixer):
+    """params: ``hidden_size``, ``num_heads``, ``num_kv_heads``, ``head_dim``, ``v_head_dim`` (default head_dim),
+    ``scale`` (default 1/sqrt(head_dim)), ``window`` (0: all keys), ``keep_first``, ``conv_taps`` (0: none), ``eps``,
+    ``unit_norm`` (default True), ``distance_penalty`` (default True), ``bias`` (default True).
+    Tensors under ``<prefix>``: q [nh*hd, H], k [nkv*hd, H], v [nkv*vd, H], each with ``.b`` and ``.conv``
+    [channels, taps]; r1, r2 [nh] (a_h, b_h); o [H, nh*vd]."""
+
+    def __init__(self, params, prefix, build):
+        super().__init__(params, prefix, build)
+        p = params
+        self.hidden = int(p["hidden_size"])
+        self.nh, self.nkv, self.hd = int(p["num_heads"]), int(p["num_kv_heads"]), int(p["head_dim"])
+        self.vd = int(p.get("v_head_dim") or self.hd)
+        self.scale = float(p["scale"]) if p.get("scale") is not None else self.hd ** -0.5
+        self.window = int(p.get("window") or 0)
+        self.keep_first = int(p.get("keep_first") or 0) if self.window else 0
+        self.taps = int(p.get("conv_taps") or 0)
+        self.eps = float(p.get("eps", 1e-6))
+        self.unit_norm = bool(p.get("unit_norm", True))
+        self.penalty = bool(p.get("distance_penalty", True))
+        self.has_bias = bool(p.get("bias", True))
+        if self.nh % self.nkv:
+            raise ValueError(f"{self.nh} query heads are not a multiple of {self.nkv} KV heads")
+        for n in (self.hd, self.vd):
+            if not 1 <= n <= 256:
+                raise ValueError(f"head size {n} is not supported: the kernels take 1 to 256")
+        self.channels = self.nh * self.hd + self.nkv * (self.hd + self.vd)
+        self.w_qkv = self.w_o = self.bias = self.conv_w = self.dist_a = self.dist_b = None
+
+    def cache_spec(self):
+        kv = CacheSpec("kv", num_kv_heads=self.nkv, head_dim=self.hd, window=self.window, keep_first=self.keep_first,
+                       v_head_dim=0 if self.vd == self.hd else self.vd)
+        if self.taps > 1:
+            return (kv, CacheSpec("state", shape=(self.taps - 1, self.channels), dtype="float32"))
+        return kv
+
+    def tensor_specs(self):
+        p, H, nh, nkv, hd, vd = self.prefix, self.hidden, self.nh, self.nkv, self.hd, self.vd
+        rows = (("q", nh * hd), ("k", nkv * hd), ("v", nkv * vd))
+        specs = [TensorSpec(p + n, (r, H)) for n, r in rows] + [TensorSpec(p + "o", (H, nh * vd))]
+        if self.has_bias:
+            specs += [TensorSpec(p + n + ".b", (r,), "bias") for n, r in rows]
+        if self.taps:
+            specs += [TensorSpec(p + n + ".conv", (r, self.taps), "bias") for n, r in rows]
+        if self.penalty:
+            specs += [TensorSpec(p + "r1", (nh,), "positive"), TensorSpec(p + "r2", (nh,), "positive")]
+        return specs
+
+    def bind(self, store):
+        p = self.prefix
+        f32 = lambda name: store.vector(p + name).float().contiguous()
+        self.w_qkv = store.matrices([p + "q", p + "k", p + "v"])
+        self.w_o = store.matrix(p + "o")
+        if self.has_bias:
+            self.bias = torch.cat([f32("q.b"), f32("k.b"), f32("v.b")]).contiguous()
+        if self.taps:
+            self.conv_w = torch.cat([f32("q.conv"), f32("k.conv"), f32("v.conv")], dim=0).contiguous()
+        if self.penalty:
+            self.dist_a, self.dist_b = f32("r1"), f32("r2")
+
+    def forward(self, x, ctx, cache, writes=True):
+        if not writes:
+            raise ValueError("this attention part keeps its own keys: it cannot read a cache another run filled")
+        kv, st = (cache[0], cache[1].state) if isinstance(cache, tuple) else (cache, None)
+        T = x.shape[0]
+        nh, nkv, hd, vd = self.nh, self.nkv, self.hd, self.vd
+        group = ctx.groups[kv.group]
+        qkv = matmul_tn(x, self.w_qkv, ctx.status, out_dtype=torch.float32, allow_partials=True)
+        q = workspace.empty((T, nh * hd), x.dtype, x.device)
+        ops.qkv_conv_norm_store(qkv, self.bias, self.conv_w, st, ctx.q_start, ctx.q_len, ctx.slots, group.slot_map, ctx.E,
+                                q, kv.pages, nh, nkv, hd, vd, self.eps, ctx.status, use_norm=self.unit_norm)
+        if self.taps > 1:
+            ops.conv_state_update(qkv, st, ctx.q_start, ctx.q_len, ctx.slots, ctx.E, bias=self.bias)
+        out = workspace.empty((T, nh * vd), x.dtype, x.device)
+        # no query reads more keys than the window and the kept first ones: no more key slices than those fill
+        reach = self.window + self.keep_first if self.window else 0
+        plan = ctx.plan(("attention", nh, nkv, "plain", reach),
+                        lambda: AttentionPlan(ctx, nh, nkv, DECODE_ROWS, SPAN_ROWS, max_keys=reach))
+        common = dict(nh=nh, nkv=nkv, hd=hd, window=self.window, status=ctx.status, table_row=ctx.slots, scale=self.scale,
+                      keep_first=self.keep_first, dist_a=self.dist_a, dist_b=self.dist_b, hd_v=vd)
+        if plan.n_dec:
+            S = plan.nslices
+            part_o = part_ml = None
+            if S > 1:
+                part_o = workspace.empty((plan.n_dec * nh * S, vd), torch.float32, x.device)
+                part_ml = workspace.empty((plan.n_dec * nh * S, 2), torch.float32, x.device)
+            ops.attn_window_bias(q, out, kv.pages, group.block_table, ctx.q_start, ctx.q_len, ctx.ctx_len, plan.dec_items,
+                                 plan.n_dec * S, DECODE_ROWS, part_o, part_ml, **common)
+            if S > 1:
+                ops.attn_merge(part_o, part_ml, plan.dec_rows, out, plan.n_dec, nh, vd, S)
+        if plan.n_span_items:
+            ops.attn_window_bias(q, out, kv.pages, group.block_table, ctx.q_start, ctx.q_len, ctx.ctx_len, plan.span_items,
+                                 plan.n_span_items, SPAN_ROWS, None, None, **common)
+        return matmul_tn(out, self.w_o, ctx.status, out_dtype=torch.float32, allow_partials=True)

@@ -122,7 +122,10 @@ def get_architecture(name: str) -> Architecture:
 
 
 def architecture_of(config_dict: dict) -> Architecture:
+    """By ``architectures[0]``, or by ``architecture`` where a config.json names just one."""
     archs = config_dict.get("architectures")
+    if archs is None and isinstance(config_dict.get("architecture"), str):
+        return get_architecture(config_dict["architecture"])
     if not isinstance(archs, list) or not archs or not isinstance(archs[0], str):
         raise ConfigError("config.json: 'architectures' must be a non-empty list of names")
     return get_architecture(archs[0])

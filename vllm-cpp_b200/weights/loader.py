@@ -29,7 +29,9 @@ class WeightError(ValueError):
 class TensorSpec:
     name: str
     shape: tuple
-    role: str = "matrix"     # "matrix" (operand of a matrix product), "vector" (gains), "table" (integers)
+    # "matrix" (operand of a matrix product), "vector" (gains), "bias" (additive terms, convolution taps), "positive"
+    # (rates that must not be negative), "table" (integers); all but the first and last are read with ``vector``
+    role: str = "matrix"
     optional: bool = False
     high: int = 0            # role "table": entries lie in [0, high) (what the random-weights mode draws from)
 

@@ -31,6 +31,10 @@ def _generate(spec: TensorSpec, seed: int, device="cpu") -> torch.Tensor:
     g.manual_seed(_tensor_seed(seed, spec.name))
     if spec.role == "vector":
         return 1.0 + GAIN_STD * torch.randn(spec.shape, generator=g, dtype=torch.float32, device=device)
+    if spec.role == "bias":       # additive terms and the taps of per-channel convolutions: around zero
+        return GAIN_STD * torch.randn(spec.shape, generator=g, dtype=torch.float32, device=device)
+    if spec.role == "positive":   # rates and strengths that must not be negative
+        return 0.05 + 0.2 * torch.randn(spec.shape, generator=g, dtype=torch.float32, device=device).abs()
     if spec.role == "table":
         if spec.high < 1:
             raise ValueError(f"integer table '{spec.name}' does not say what range its entries have (TensorSpec.high)")
