@@ -1,7 +1,7 @@
 #!/usr/bin/env python3
 """Benchmark of the engine on one B200.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--workloads all|headline] [--impl reference]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--workloads all|headline|14b|4b|rimopel] [--impl reference]
 
 Headline: decode tokens/s of the Qwen3-8B layer sizes (the baseline's third configuration) at batch 8 and context
 4,096, the median of K device-timed steps after W warm-up steps; beside it batch 1 and 64, batch 8 at context 2,176
@@ -437,6 +437,136 @@ def run_4b(args, pk, clocks, windows):
     return out
 
 
+# ------------------------------------------------------------------------------------------------ Rimopel beside Qwen3
+# Layer sizes of real models (random weights): width, heads, KV heads, head size, the dense feed-forward's hidden size and
+# the SwiGLU hidden size with as many parameters, window, layers.
+RIMOPEL_SIZES = {
+    "w2048": dict(width=2048, heads=16, kv_heads=4, dim=128, ff=8192, swiglu=5504, window=1024, layers=12, vocab=32768),
+    "w4096": dict(width=4096, heads=32, kv_heads=8, dim=128, ff=16384, swiglu=10944, window=2048, layers=8, vocab=32768),
+}
+
+
+def run_rimopel(args, pk, clocks, windows):
+    """Prefill (one prompt of 2,048 tokens in one step) and decode (batch 8 behind a context of 4,096 tokens, captured
+    steps) of Rimopel at real layer sizes, beside Qwen3 with the same width, heads, window on every layer, layer count and
+    feed-forward parameter count: tokens/s, the fraction of the measured roofline, and the time per group of kernels."""
+    import numpy as np
+    import torch
+    from vllm_cpp_b200 import EngineConfig, LLM, Qwen3Config, ops
+    from vllm_cpp_b200.config.rimopel import RimopelConfig, RimopelLayer, RimopelMixer
+    from vllm_cpp_b200.engine.step import StepEntry
+    from vllm_cpp_b200.runtime import runtime
+
+    rt = runtime()
+    rng = np.random.default_rng(0)
+    B, context, T = args.batch, args.context, PREFILL_TOKENS
+    out = {"workload": "rimopel_beside_qwen3", "batch": B, "context": context, "prefill_tokens": T, "peaks": pk["source"],
+           "data": "synthetic (random weights, uniform random token ids, random cache contents for the held context)",
+           "l2": "inputs (over 1 GB of weights) larger than L2", "timing": "median of steps, CUDA events", "sizes": {}}
+
+    def configs(z):
+        mixer = RimopelMixer(heads=z["heads"], kv_heads=z["kv_heads"], dim=z["dim"], vdim=z["dim"], scale=z["dim"] ** -0.5, conv=3,
+                             window=z["window"], keep_first=4)
+        rim = RimopelConfig(vocab=z["vocab"], width=z["width"], norm_eps=1e-5, canon_taps=3, max_positions=context + 4096,
+                            layers=tuple(RimopelLayer("attention", mixer, "dense", z["ff"]) for _ in range(z["layers"])))
+        qwen = Qwen3Config(vocab_size=z["vocab"], hidden_size=z["width"], intermediate_size=z["swiglu"], num_hidden_layers=z["layers"],
+                           num_attention_heads=z["heads"], num_key_value_heads=z["kv_heads"], head_dim=z["dim"],
+                           max_position_embeddings=context + 4096, rms_norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=False,
+                           sliding_window=z["window"], layer_types=("sliding_attention",) * z["layers"])
+        return {"rimopel": rim, "qwen3": qwen}
+
+    def numbers(z, name):
+        W, H, G, d, L, V = z["width"], z["heads"], z["kv_heads"], z["dim"], z["layers"], z["vocab"]
+        attn = (H + 2 * G) * d * W + W * H * d
+        layer = attn + (2 * z["ff"] * W + 2 * W * W if name == "rimopel" else 3 * z["swiglu"] * W)
+        keys = min(context, z["window"])
+        return dict(weight_bytes=2 * (L * layer + V * W), kv_bytes=L * 2 * G * d * 2 * keys,
+                    prefill_flops=2.0 * T * L * layer + 2.0 * V * W + L * 4.0 * H * d * sum(min(i + 1, z["window"]) for i in range(T)))
+
+    def measure(cfg, z, name, profile):
+        per_req = -(-(context + args.steps + args.warmup + 8) // 64) * 64
+        max_tokens = max(B * per_req, T + 64)
+        llm = LLM(config=cfg, random_seed=0, engine=EngineConfig(dtype="bfloat16", page_size=PAGE, max_tokens=max_tokens, max_num_seqs=B,
+                                                                max_step_tokens=T, max_model_len=context + 4096, profile=profile))
+        runner = llm.runner
+        V = z["vocab"]
+        for t in runner.cache.tensors:
+            for i in range(t.shape[0]):
+                t[i].normal_(0, 1)
+        n_groups = len(runner.layout.paged)
+
+        def fresh():
+            runner.reset_tables()
+            return rt.CacheManager(runner.layout.runtime_groups(rt, PAGE, max_tokens // PAGE), B)
+
+        def timed(fn, n, warm):
+            times = []
+            for it in range(warm + n):
+                if it == warm:
+                    windows.append([clocks.mark(), None])
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                ent = fn()
+                e0.record()
+                runner.step(ent, check=False)
+                e1.record()
+                e1.synchronize()
+                times.append(e0.elapsed_time(e1))
+            windows[-1][1] = clocks.mark()
+            return statistics.median(times[warm:])
+
+        def prefill_entry():
+            cm = fresh()
+            cm.open(0)
+            assert cm.reserve(0, T)
+            return [StepEntry(cm.slot(0), 0, rng.integers(0, V, T).tolist(), [cm.block_table(0, g) for g in range(n_groups)], [T - 1])]
+
+        res = {}
+        if profile:
+            runner.profile.clear()
+        l0 = ops.launch_count
+        pf_ms = timed(prefill_entry, 5, 3)
+        res["prefill_launches"] = (ops.launch_count - l0) // 8
+        if profile:
+            res["prefill_groups_ms"] = {k: round(v / 8, 4) for k, v in sorted(runner.profile.items())}
+            runner.profile.clear()
+        cm = fresh()
+        for r in range(B):
+            cm.open(r)
+            assert cm.reserve(r, context + args.steps + args.warmup + 1)
+            cm.commit(r, context)
+
+        def decode_entries():
+            ent = []
+            for r in range(B):
+                pos = cm.num_tokens(r)
+                ent.append(StepEntry(cm.slot(r), pos, [int(rng.integers(0, V))], [cm.block_table(r, g) for g in range(n_groups)], [0]))
+                cm.commit(r, pos + 1)
+            return ent
+
+        dec_ms = timed(decode_entries, args.steps, args.warmup)
+        if profile:
+            res["decode_groups_ms"] = {k: round(v / (args.steps + args.warmup), 4) for k, v in sorted(runner.profile.items())}
+        ops.check_status(runner.status)
+        n = numbers(z, name)
+        res.update(prefill_ms=pf_ms, prefill_tokens_per_s=T * 1000.0 / pf_ms,
+                   prefill_frac_of_bf16_peak=n["prefill_flops"] / (pf_ms * 1e-3) / (pk["bf16_tflops"] * 1e12),
+                   decode_ms=dec_ms, decode_tokens_per_s=B * 1000.0 / dec_ms,
+                   decode_frac_of_hbm_peak=(n["weight_bytes"] + B * n["kv_bytes"]) / (dec_ms * 1e-3) / 1e9 / pk["hbm_gbs"])
+        del llm, runner
+        release()
+        return res
+
+    for size, z in RIMOPEL_SIZES.items():
+        out["sizes"][size] = {"config": z}
+        for name, cfg in configs(z).items():
+            r = measure(cfg, z, name, profile=False)
+            p = measure(cfg, z, name, profile=True)      # kernel by kernel, with events between the groups of kernels
+            r["prefill_groups_ms"], r["decode_groups_ms"] = p["prefill_groups_ms"], p["decode_groups_ms"]
+            r["prefill_launches"] = p["prefill_launches"]
+            out["sizes"][size][name] = r
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -448,8 +578,9 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=CONTEXT)
     ap.add_argument("--impl", default="ours")
-    ap.add_argument("--workloads", default="all", choices=["all", "headline", "14b", "4b"],
-                    help="headline: the 8B numbers only; 14b / 4b: that workload alone (prints its own JSON line)")
+    ap.add_argument("--workloads", default="all", choices=["all", "headline", "14b", "4b", "rimopel"],
+                    help="headline: the 8B numbers only; 14b / 4b: that workload alone (prints its own JSON line); rimopel: "
+                         "Rimopel at real layer sizes beside Qwen3 at equal size, prefill and decode (its own JSON line)")
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch (for profiling runs)")
     ap.add_argument("--no-graphs", action="store_true", help="launch decode steps kernel by kernel (for profiling runs)")
     ap.add_argument("--mode", default="all", choices=["all", "decode", "prefill"], help="what to run (profiling runs)")
@@ -471,8 +602,8 @@ def main():
     clocks.start()
     windows = []
     try:
-        if args.workloads in ("14b", "4b"):
-            out = (run_14b if args.workloads == "14b" else run_4b)(args, pk, clocks, windows)
+        if args.workloads in ("14b", "4b", "rimopel"):
+            out = {"14b": run_14b, "4b": run_4b, "rimopel": run_rimopel}[args.workloads](args, pk, clocks, windows)
             out["clocks"] = clocks.summary(windows)
             print(json.dumps(out))
             return 0

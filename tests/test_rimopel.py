@@ -356,10 +356,23 @@ def test_activation_of_partial_sums(kind):
 
 
 def run_window_attention(dtype, nh, nkv, d, dv, ps, window, keep, shapes, craft=None, penalty=True, scale=0.3):
+    """Runs the plain kernel, and the tensor-core kernel too (with TMA tile loads, with cp.async loads, and with a
+    token's key slices merged within a cluster) where it takes the type and the head sizes."""
+    from vllm_cpp_b200 import ops
+    plan = _run_window_attention(dtype, nh, nkv, d, dv, ps, window, keep, shapes, craft, penalty, scale, "plain")
+    if d == dv and ops.attn_mma_supported(dtype, d):
+        for kernel in ("mma", "mma_no_tma", "mma_cluster"):
+            plan = _run_window_attention(dtype, nh, nkv, d, dv, ps, window, keep, shapes, craft, penalty, scale, kernel)
+    return plan
+
+
+def _run_window_attention(dtype, nh, nkv, d, dv, ps, window, keep, shapes, craft, penalty, scale, kernel):
     """shapes: [(tokens cached before the step, query tokens of the step)]; compares the kernel (decoded tokens with
     sliced key ranges, prompt portions in query tiles) with the plain attention of one head at a time."""
     from vllm_cpp_b200 import ops
     from vllm_cpp_b200.parts import attention as A
+    mma = kernel != "plain"
+    DEC, SPAN = (A.MMA_DECODE_ROWS, A.MMA_SPAN_ROWS) if mma else (A.DECODE_ROWS, A.SPAN_ROWS)
     g = torch.Generator().manual_seed(5)
     a = (0.05 + torch.rand(nh, generator=g, dtype=torch.float64) * 2).float() if penalty else None
     b = (0.05 + torch.rand(nh, generator=g, dtype=torch.float64) * 0.3).float() if penalty else None
@@ -397,7 +410,7 @@ def run_window_attention(dtype, nh, nkv, d, dv, ps, window, keep, shapes, craft=
     ctx.host_q_len = [n for _, n in shapes]
     ctx.host_ctx_len = [s + n for s, n in shapes]
     ctx.host_q_start = [int(x) for x in np.cumsum([0] + ctx.host_q_len[:-1])]
-    plan = A.AttentionPlan(ctx, nh, nkv, A.DECODE_ROWS, A.SPAN_ROWS, max_keys=(window + keep) if window else 0)
+    plan = A.AttentionPlan(ctx, nh, nkv, DEC, SPAN, d if kernel == "mma_cluster" else None, max_keys=(window + keep) if window else 0)
     E, T = len(shapes), sum(ctx.host_q_len)
     bt = torch.full((E, max(len(t) for t in tables)), -1, dtype=torch.int32)
     for i, t in enumerate(tables):
@@ -406,16 +419,22 @@ def run_window_attention(dtype, nh, nkv, d, dv, ps, window, keep, shapes, craft=
     status = torch.zeros(1, dtype=torch.int32, device=dev())
     q_flat = torch.cat(qs).to(dtype).to(dev()).view(T, nh * d)
     args = (pages, bt.to(dev()), i32(ctx.host_q_start), i32(ctx.host_q_len), i32(ctx.host_ctx_len))
-    opts = dict(scale=scale, keep_first=keep, dist_a=None if a is None else a.to(dev()), dist_b=None if b is None else b.to(dev()), hd_v=dv)
+    opts = dict(scale=scale, keep_first=keep, dist_a=None if a is None else a.to(dev()), dist_b=None if b is None else b.to(dev()))
+    if mma:
+        run = lambda *x, **k: ops.attn_mma(*x, allow_tma=kernel != "mma_no_tma", **k, **opts)
+    else:
+        run = lambda *x, **k: ops.attn_window_bias(*x, hd_v=dv, **opts)
     if plan.n_dec:
         S = plan.nslices
-        po = torch.empty(plan.n_dec * nh * S, dv, device=dev()) if S > 1 else None
-        pm = torch.empty(plan.n_dec * nh * S, 2, device=dev()) if S > 1 else None
-        ops.attn_window_bias(q_flat, out, *args, plan.dec_items, plan.n_dec * S, A.DECODE_ROWS, po, pm, nh, nkv, d, window, status, **opts)
-        if S > 1:
+        cluster = plan.cluster if kernel == "mma_cluster" else 0
+        po = torch.empty(plan.n_dec * nh * S, dv, device=dev()) if S > 1 and not cluster else None
+        pm = torch.empty(plan.n_dec * nh * S, 2, device=dev()) if S > 1 and not cluster else None
+        run(q_flat, out, *args, plan.dec_items, plan.n_dec * S, DEC, po, pm, nh, nkv, d, window, status,
+            slice_counters=plan.slice_counters if S > 1 else None, dec_rows=plan.dec_rows, cluster=cluster)
+        if S > 1 and not mma:
             ops.attn_merge(po, pm, plan.dec_rows, out, plan.n_dec, nh, dv, S)
     if plan.n_span_items:
-        ops.attn_window_bias(q_flat, out, *args, plan.span_items, plan.n_span_items, A.SPAN_ROWS, None, None, nh, nkv, d, window, status, **opts)
+        run(q_flat, out, *args, plan.span_items, plan.n_span_items, SPAN, None, None, nh, nkv, d, window, status)
     torch.cuda.synchronize()
     assert status.item() == 0
     got = out.double().cpu().view(T, nh, dv)
@@ -433,7 +452,8 @@ def run_window_attention(dtype, nh, nkv, d, dv, ps, window, keep, shapes, craft=
 
 @gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("nh,nkv,d,dv,ps", [(4, 2, 16, 24, 4), (3, 3, 20, 12, 8), (8, 2, 64, 64, 16), (2, 1, 128, 32, 16), (40, 1, 8, 256, 5)])
+@pytest.mark.parametrize("nh,nkv,d,dv,ps", [(4, 2, 16, 24, 4), (3, 3, 20, 12, 8), (8, 2, 64, 64, 16), (2, 1, 128, 32, 16), (40, 1, 8, 256, 5),
+                                            (4, 1, 128, 128, 8), (6, 3, 64, 64, 5)])
 def test_window_attention_mixed_batch(dtype, nh, nkv, d, dv, ps):
     """Decoded tokens beside prompt portions: at the very start, before the window is full, far beyond it."""
     shapes = [(0, 1), (0, 7), (3, 1), (11, 1), (30, 2), (64, 33), (300, 1), (250, 70), (1, 2)]
@@ -445,7 +465,7 @@ def test_window_attention_mixed_batch(dtype, nh, nkv, d, dv, ps):
 @gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("which", ["kept_last", "first_not_kept", "window_first", "before_window", "position_0"])
-@pytest.mark.parametrize("d,dv,ps", [(24, 40, 8), (64, 64, 16)])
+@pytest.mark.parametrize("d,dv,ps", [(24, 40, 8), (64, 64, 16), (128, 128, 32)])
 def test_one_key_stands_out_at_every_edge(dtype, which, d, dv, ps):
     """A key whose score dominates: the last kept first key and the window's first key must count, the first key that is
     not kept and the key just before the window must not, for a decoded token and inside a prompt portion."""
@@ -458,6 +478,16 @@ def test_one_key_stands_out_at_every_edge(dtype, which, d, dv, ps):
             k[j] = q[-1, 0] * 1.0          # cosine 1 with the last query's first head
             v[j] = 50.0
         run_window_attention(dtype, 2, 2, d, dv, ps, W, keep, [(start, n)], craft, scale=40.0 / d)
+
+
+@gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_many_kept_first_keys_and_long_windows(dtype):
+    """More kept first keys than one key tile holds, before a window of several tiles; a window of two keys."""
+    shapes = [(2000, 1), (1500, 140), (100, 1), (60, 30), (0, 300)]
+    run_window_attention(dtype, 4, 2, 64, 64, 16, 300, 150, shapes)
+    run_window_attention(dtype, 4, 4, 128, 128, 16, 2, 1, shapes[1:4])
+    run_window_attention(dtype, 2, 1, 64, 64, 8, 1, 70, shapes[2:4])
 
 
 @gpu

@@ -78,6 +78,12 @@ struct AttnArgs {
     int* status;
     FusedQkv f;
     int cluster;   // > 1: the blocks of a token's key slices form a cluster of that many and merge through shared memory
+    // Options of other designs (off: 0, null).  With a window, the first keep_first keys of a request stay visible to
+    // every later query: the first key slice reads those that lie before the item's window as tiles of their own,
+    // ahead of its range.  dist_a, dist_b [nh]: a_h ln(1 + b_h (pos - j)) is taken off the score of key j.
+    int keep_first;
+    const float* dist_a;
+    const float* dist_b;
 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
@@ -216,7 +222,15 @@ __global__ __launch_bounds__(WR * WK * 32 + (TMA ? 32 : 0)) void attn_mma_kernel
     const int k_begin = max(lo, my_pb_lo * ps), k_end = min(hi, my_pb_hi * ps);
     // tiles start on a page boundary when TMA loads whole pages
     const int t_first = TMA ? my_pb_lo * ps : k_begin;
-    const int n_tiles = k_end > k_begin ? (k_end - t_first + BN - 1) / BN : 0;
+    const int n_own = k_end > k_begin ? (k_end - t_first + BN - 1) / BN : 0;   // tiles of the slice's own key range
+    // kept first keys before the item's window: tiles 0 .. n_ft - 1 hold keys [0, n_first), the slice's own follow
+    const int KF = W > 0 ? a.keep_first : 0;
+    const int n_first = slice == 0 ? min(KF, lo) : 0;
+    const int n_ft = (n_first + BN - 1) / BN;
+    const int n_tiles = n_ft + n_own;
+    auto tile_t0 = [&](int it) { return it < n_ft ? it * BN : t_first + (it - n_ft) * BN; };
+    auto tile_beg = [&](int it) { return it < n_ft ? 0 : k_begin; };
+    auto tile_end = [&](int it) { return it < n_ft ? n_first : k_end; };
 
     const int* bt = a.block_table + (size_t)(a.table_row ? a.table_row[e] : e) * a.max_blocks;
 
@@ -237,9 +251,12 @@ __global__ __launch_bounds__(WR * WK * 32 + (TMA ? 32 : 0)) void attn_mma_kernel
     const int groups_page = ps / 8;
     const int groups_kv = a.nkv * groups_page;   // groups of 8 rows from a page's K to its V
     const int my_pg = lane >> 1, my_v = lane & 1;
+    const int first_pb_hi = (n_first + ps - 1) / ps;   // pages that hold the kept first keys read here
+    auto tile_pb0 = [&](int it) { return it < n_ft ? it * pages_per_tile : my_pb_lo + (it - n_ft) * pages_per_tile; };
+    auto tile_pb_hi = [&](int it) { return it < n_ft ? first_pb_hi : my_pb_hi; };
     auto page_of = [&](int it) {
-        const int pb = my_pb_lo + it * pages_per_tile + my_pg;
-        return (it < n_tiles && my_pg < pages_per_tile && pb < my_pb_hi) ? bt[pb] : -1;
+        const int pb = tile_pb0(it) + my_pg;
+        return (it < n_tiles && my_pg < pages_per_tile && pb < tile_pb_hi(it)) ? bt[pb] : -1;
     };
     // page ids of the next AHEAD tiles, read that far ahead: each is a load from the block table, and read only one
     // tile ahead they made the tiles of a short key range (a few tiles, nothing else to wait for) follow each other
@@ -257,8 +274,8 @@ __global__ __launch_bounds__(WR * WK * 32 + (TMA ? 32 : 0)) void attn_mma_kernel
         bool ok = true;
         if (lane == 0) ok = mbar_wait(empty_bar(st), ((it / STAGES) & 1) ^ 1u, abort_flag, a.status);
         if (!__shfl_sync(0xffffffffu, ok, 0)) return false;
-        const int pb0 = my_pb_lo + it * pages_per_tile;
-        const int np = min(pages_per_tile, my_pb_hi - pb0);
+        const int pb0 = tile_pb0(it);
+        const int np = min(pages_per_tile, tile_pb_hi(it) - pb0);
         if (lane == 0) mbar_expect_tx(full_bar(st), (uint32_t)(np * ps * ROWB * 2));
         __syncwarp();
         if (my_pg < np) {
@@ -288,7 +305,7 @@ __global__ __launch_bounds__(WR * WK * 32 + (TMA ? 32 : 0)) void attn_mma_kernel
 #pragma unroll
             for (int k = 0; k < AHEAD; ++k) ahead_page[k] = page_of(k);
             while (pre_tiles < n_tiles && pre_tiles < STAGES &&
-                   min(my_pb_hi, my_pb_lo + (pre_tiles + 1) * pages_per_tile) * ps <= first_new) {
+                   min(tile_pb_hi(pre_tiles), tile_pb0(pre_tiles) + pages_per_tile) * ps <= first_new) {
                 if (!issue_tile(pre_tiles)) break;
                 ++pre_tiles;
             }
@@ -440,7 +457,7 @@ __global__ __launch_bounds__(WR * WK * 32 + (TMA ? 32 : 0)) void attn_mma_kernel
     }
 
     // ---- cp.async loader (all threads): 64 keys x HD of K and of V, gathered page by page ----
-    auto load_tile = [&](int stage, int t0) {
+    auto load_tile = [&](int stage, int t0, int t_end) {
         uint8_t* kd = k_s + stage * TILE_BYTES;
         uint8_t* vd = v_s + stage * TILE_BYTES;
 #pragma unroll
@@ -450,7 +467,7 @@ __global__ __launch_bounds__(WR * WK * 32 + (TMA ? 32 : 0)) void attn_mma_kernel
             const int kidx = t0 + j;
             const __nv_bfloat16* src = a.pages;
             int bytes = 0;
-            if (kidx < k_end) {
+            if (kidx < t_end) {
                 const int page = bt[kidx / ps];
                 if (page < 0 || page >= a.num_pages) {
                     atomicOr(a.status, VCB_STATUS_BAD_PAGE);
@@ -466,7 +483,7 @@ __global__ __launch_bounds__(WR * WK * 32 + (TMA ? 32 : 0)) void attn_mma_kernel
     };
 
     if (!TMA) {
-        if (n_tiles > 0) load_tile(0, t_first);
+        if (n_tiles > 0) load_tile(0, tile_t0(0), tile_end(0));
         cp_async_commit();
     }
     __syncthreads();   // Q and the barriers are in shared memory
@@ -502,6 +519,16 @@ __global__ __launch_bounds__(WR * WK * 32 + (TMA ? 32 : 0)) void attn_mma_kernel
         ok_a[mr] = r_a[mr] < R;
         ok_b[mr] = r_a[mr] + 8 < R;
     }
+    float da_a[MR], db_a[MR], da_b[MR], db_b[MR];   // the distance penalty's a_h, b_h of rows a and b
+#pragma unroll
+    for (int mr = 0; mr < MR; ++mr) {
+        const bool on = a.dist_a != nullptr;
+        const int ha = head0 + r_a[mr] % gq, hb = head0 + (r_a[mr] + 8) % gq;
+        da_a[mr] = on && ok_a[mr] ? a.dist_a[ha] : 0.f;
+        db_a[mr] = on && ok_a[mr] ? a.dist_b[ha] : 0.f;
+        da_b[mr] = on && ok_b[mr] ? a.dist_a[hb] : 0.f;
+        db_b[mr] = on && ok_b[mr] ? a.dist_b[hb] : 0.f;
+    }
 
     if (warp < NW) {
         // ---- one 16-row tile per warp: its Q fragments stay in registers; two: they are re-read per key tile ----
@@ -514,21 +541,22 @@ __global__ __launch_bounds__(WR * WK * 32 + (TMA ? 32 : 0)) void attn_mma_kernel
 
         for (int it = 0; it < n_tiles; ++it) {
             const int st = it % STAGES;
-            const int t0 = t_first + it * BN;
+            const int t0 = tile_t0(it);
+            const int kb = tile_beg(it), ke = tile_end(it);   // the keys of this tile that count
             if (TMA) {
                 if (!mbar_wait(full_bar(st), (it / STAGES) & 1, abort_flag, a.status)) break;
-                if (t0 + BN > k_end) {
+                if (t0 + BN > ke) {
                     // the last page may hold slots beyond the sequence (and rows of pages not loaded are stale):
                     // their V must be finite, because a zero weight times NaN is NaN.  Each warp clears what it reads.
                     for (int idx = lane; idx < KW * CH; idx += 32) {
                         const int j = wk * KW + idx / CH, c = idx % CH;
-                        if (t0 + j >= k_end) *reinterpret_cast<uint4*>(v_s + st * TILE_BYTES + swz_kv<HD / 64>(j, c)) = make_uint4(0, 0, 0, 0);
+                        if (t0 + j >= ke) *reinterpret_cast<uint4*>(v_s + st * TILE_BYTES + swz_kv<HD / 64>(j, c)) = make_uint4(0, 0, 0, 0);
                     }
                     __syncwarp();
                 }
             } else {
                 if (it + 1 < n_tiles) {
-                    load_tile((it + 1) & 1, t0 + BN);
+                    load_tile((it + 1) & 1, tile_t0(it + 1), tile_end(it + 1));
                     cp_async_commit();
                     cp_async_wait<1>();
                 } else {
@@ -573,7 +601,8 @@ __global__ __launch_bounds__(WR * WK * 32 + (TMA ? 32 : 0)) void attn_mma_kernel
             }
             // mask (only where the tile touches an edge of some row's key range), running maximum
             // rows beyond R hold zero queries and are never written, so they need no mask of their own
-            const bool inner = key0 >= k_begin && key0 + KW <= k_end && key0 + KW - 1 <= pos0 && (W <= 0 || key0 > pos_last - W);
+            const bool inner = a.dist_a == nullptr && key0 >= kb && key0 + KW <= ke && key0 + KW - 1 <= pos0 &&
+                               (W <= 0 || key0 > pos_last - W || key0 + KW <= KF);
             const bool all_inner = __all_sync(0xffffffffu, inner);
             uint32_t pa[MR][KW / 16][4];
 #pragma unroll
@@ -596,11 +625,18 @@ __global__ __launch_bounds__(WR * WK * 32 + (TMA ? 32 : 0)) void attn_mma_kernel
 #pragma unroll
                         for (int c = 0; c < 2; ++c) {
                             const int kidx = key0 + i * 8 + 2 * (lane & 3) + c;
-                            const bool in = kidx >= k_begin && kidx < k_end;
-                            const bool sa = ok_a[mr] && in && kidx <= pos_a[mr] && (W <= 0 || kidx > pos_a[mr] - W);
-                            const bool sb = ok_b[mr] && in && kidx <= pos_b[mr] && (W <= 0 || kidx > pos_b[mr] - W);
-                            s[mr][i][c] = sa ? s[mr][i][c] * a.scale : -CUDART_INF_F;
-                            s[mr][i][2 + c] = sb ? s[mr][i][2 + c] * a.scale : -CUDART_INF_F;
+                            const bool in = kidx >= kb && kidx < ke;
+                            const bool sa = ok_a[mr] && in && kidx <= pos_a[mr] && (W <= 0 || kidx > pos_a[mr] - W || kidx < KF);
+                            const bool sb = ok_b[mr] && in && kidx <= pos_b[mr] && (W <= 0 || kidx > pos_b[mr] - W || kidx < KF);
+                            float va = s[mr][i][c] * a.scale, vb = s[mr][i][2 + c] * a.scale;
+                            if (a.dist_a != nullptr) {
+                                // the penalty of the distance (ln through the fast base-2 logarithm: its error, some 1e-6,
+                                // is far below the rounding of the bfloat16 operands)
+                                if (sa) va -= da_a[mr] * __logf(fmaf(db_a[mr], (float)(pos_a[mr] - kidx), 1.f));
+                                if (sb) vb -= da_b[mr] * __logf(fmaf(db_b[mr], (float)(pos_b[mr] - kidx), 1.f));
+                            }
+                            s[mr][i][c] = sa ? va : -CUDART_INF_F;
+                            s[mr][i][2 + c] = sb ? vb : -CUDART_INF_F;
                             mx_a = fmaxf(mx_a, s[mr][i][c]);
                             mx_b = fmaxf(mx_b, s[mr][i][2 + c]);
                         }
@@ -661,7 +697,7 @@ __global__ __launch_bounds__(WR * WK * 32 + (TMA ? 32 : 0)) void attn_mma_kernel
                 }
             }
             if (TMA) {
-                if (t0 + BN > k_end) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the clearing stores above
+                if (t0 + BN > ke) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the clearing stores above
                 __syncwarp();
                 if (lane == 0) mbar_arrive(empty_bar(st));   // this warp is done with the stage
             } else {
@@ -1008,20 +1044,40 @@ bool vcb_kv_tensor_map(const void* pages, long long rows, int hd, int page_size,
 // Only bfloat16 and head_dim 64 or 128; the caller falls back to vcb_attn_paged otherwise.
 VCB_API int vcb_attn_mma_supported(int dtype, int hd) { return dtype == VCB_BF16 && (hd == 64 || hd == 128); }
 
+VCB_API int vcb_attn_mma_ex(const void* q, void* out, const void* pages, long long page_stride, const int* block_table,
+                            const int* table_row, int max_blocks, const int* q_start, const int* q_len,
+                            const int* ctx_len, const int* items, int n_items, int rows_max, float* part_o,
+                            float* part_ml, int* slice_counters, const int* dec_rows, int nh, int nkv, int hd,
+                            int page_size, int num_pages, int window, float scale, int keep_first, const float* dist_a,
+                            const float* dist_b, int* status, int allow_tma, int cluster, cudaStream_t stream);
+
 VCB_API int vcb_attn_mma(const void* q, void* out, const void* pages, long long page_stride, const int* block_table,
                          const int* table_row, int max_blocks, const int* q_start, const int* q_len,
                          const int* ctx_len, const int* items, int n_items, int rows_max, float* part_o,
                          float* part_ml, int* slice_counters, const int* dec_rows, int nh, int nkv, int hd,
                          int page_size, int num_pages, int window, float scale, int* status, int allow_tma,
                          int cluster, cudaStream_t stream) {
+    return vcb_attn_mma_ex(q, out, pages, page_stride, block_table, table_row, max_blocks, q_start, q_len, ctx_len, items,
+                           n_items, rows_max, part_o, part_ml, slice_counters, dec_rows, nh, nkv, hd, page_size, num_pages,
+                           window, scale, 0, nullptr, nullptr, status, allow_tma, cluster, stream);
+}
+
+// keep_first, dist_a, dist_b: the options described with AttnArgs.
+VCB_API int vcb_attn_mma_ex(const void* q, void* out, const void* pages, long long page_stride, const int* block_table,
+                            const int* table_row, int max_blocks, const int* q_start, const int* q_len,
+                            const int* ctx_len, const int* items, int n_items, int rows_max, float* part_o,
+                            float* part_ml, int* slice_counters, const int* dec_rows, int nh, int nkv, int hd,
+                            int page_size, int num_pages, int window, float scale, int keep_first, const float* dist_a,
+                            const float* dist_b, int* status, int allow_tma, int cluster, cudaStream_t stream) {
     if (n_items == 0) return 0;
+    VCB_CHECK_ARG(keep_first >= 0 && (dist_a == nullptr) == (dist_b == nullptr), "attn_mma: bad keep_first %d or half a distance penalty", keep_first);
     VCB_CHECK_ARG(nh > 0 && nkv > 0 && nh % nkv == 0, "attn_mma: %d query heads are not a multiple of %d KV heads", nh, nkv);
     VCB_CHECK_ARG(hd == 64 || hd == 128, "attn_mma: head_dim %d is not 64 or 128", hd);
     VCB_CHECK_ARG(rows_max == 16 || rows_max == 128, "attn_mma: rows_max must be 16 or 128");
     VCB_CHECK_ARG(page_size > 0 && window >= 0, "attn_mma: bad page_size %d or window %d", page_size, window);
     AttnArgs a{(const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)pages, page_stride, block_table,
                table_row, max_blocks, q_start, q_len, ctx_len, items, part_o, part_ml, slice_counters, dec_rows, nh, nkv,
-               page_size, num_pages, window, scale, status, FusedQkv{}, cluster};
+               page_size, num_pages, window, scale, status, FusedQkv{}, cluster, keep_first, dist_a, dist_b};
     const bool tma = allow_tma && (page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64) &&
                      ((uintptr_t)pages % 16 == 0) && page_stride == (long long)2 * nkv * page_size * hd;
     if (hd == 64) return tma ? launch_rows<64, true>(a, n_items, rows_max, stream) : launch_rows<64, false>(a, n_items, rows_max, stream);

@@ -80,6 +80,7 @@ def _declare(L):
         "vcb_selftest_wait_timeout": [LL, P, P, P],
         "vcb_state_reset": [P, I, LL, LL, LL, I, I, P, P, P, I, ctypes.c_uint, P, P],
         "vcb_attn_mma": [P, P, P, LL, P, P, I, P, P, P, P, I, I, P, P, P, P, I, I, I, I, I, I, F, P, I, I, P],
+        "vcb_attn_mma_ex": [P, P, P, LL, P, P, I, P, P, P, P, I, I, P, P, P, P, I, I, I, I, I, I, F, I, P, P, P, I, I, P],
         "vcb_attn_mma_supported": [I, I],
         "vcb_attn_mma_max_clusters": [I, I, I],
         "vcb_attn_mma_fused_supported": [I, I, I],
@@ -666,8 +667,9 @@ def attn_tc(q, out, pages, block_table, q_start, q_len, ctx_len, items, n_items,
 
 def attn_mma(q, out, pages, block_table, q_start, q_len, ctx_len, items, n_items, rows_max, part_o, part_ml,
              nh, nkv, hd, window, status, table_row=None, allow_tma=True, slice_counters=None, dec_rows=None,
-             cluster=0):
-    """Tensor-core variant of :func:`attn_paged` (bfloat16, head_dim 64 or 128; rows_max 16 or 128).
+             cluster=0, scale=None, keep_first=0, dist_a=None, dist_b=None):
+    """Tensor-core variant of :func:`attn_paged` (bfloat16, head_dim 64 or 128; rows_max 16 or 128), with the
+    options of :func:`attn_window_bias` (``scale``, default 1/sqrt(hd); ``keep_first``; ``dist_a``/``dist_b``).
     With ``slice_counters`` (int32 zeros, one per decoded token and KV head group, left at zero again) and
     ``dec_rows``, the block that finishes a token's last key slice merges the slices itself; with ``cluster`` = the
     number of slices per token (2 to 8) as well, the slices' blocks run as a cluster and merge through shared memory."""
@@ -677,10 +679,14 @@ def attn_mma(q, out, pages, block_table, q_start, q_len, ctx_len, items, n_items
         _need(t, name, torch.int32)
     num_pages, two, nkv_p, page_size, hd_p = pages.shape
     assert two == 2 and nkv_p == nkv and hd_p == hd
-    _call("vcb_attn_mma", _p(q), _p(out), _p(pages), pages.stride(0), _p(block_table), _p(table_row),
+    if dist_a is not None:
+        _need(dist_a, "dist_a", torch.float32); _need(dist_b, "dist_b", torch.float32)
+        assert dist_a.numel() == nh and dist_b.numel() == nh
+    _call("vcb_attn_mma_ex", _p(q), _p(out), _p(pages), pages.stride(0), _p(block_table), _p(table_row),
           block_table.shape[1], _p(q_start), _p(q_len), _p(ctx_len), _p(items), n_items, rows_max, _p(part_o),
           _p(part_ml), _p(slice_counters), _p(dec_rows), nh, nkv, hd, page_size, num_pages, int(window or 0),
-          1.0 / math.sqrt(hd), _p(status), int(allow_tma), int(cluster), _stream())
+          1.0 / math.sqrt(hd) if scale is None else float(scale), int(keep_first or 0), _p(dist_a), _p(dist_b), _p(status),
+          int(allow_tma), int(cluster), _stream())
 
 
 def attn_stream_supported(dtype: torch.dtype, hd: int, page_size: int, nh: int, nkv: int) -> bool:

@@ -14,17 +14,24 @@ bias, no convolution, no norm, no penalty, no window), so the part serves other 
 Per request the part keeps the keys and values in pages (given back as the window passes, except the pages of the
 kept first keys) and, for the convolution, the last taps - 1 rows of the stacked projection as a fixed-size state.
 Scores, softmax, the penalty, the norms and the convolution are 32-bit; keys, values and queries are stored in the
-compute dtype.
+compute dtype.  In bfloat16 with keys and values of 64 or 128 lanes the scores and the weighted sums run on the
+tensor cores (the kernel of the rotary attention part, with these options); otherwise on the plain kernel.
 """
 from __future__ import annotations
+
+import os
 
 import torch
 
 from .. import ops, workspace
 from ..weights.loader import TensorSpec
-from .attention import DECODE_ROWS, SPAN_ROWS, AttentionPlan
+from .attention import CLUSTER_MERGE, DECODE_ROWS, MMA_DECODE_ROWS, MMA_SPAN_ROWS, SPAN_ROWS, AttentionPlan
 from .base import CacheSpec, Mixer
 from .linear import matmul_tn
+
+
+# 0 keeps every step on the plain attention kernel (comparison runs, tests)
+MMA_ATTENTION = os.environ.get("VLLM_CPP_B200_WINDOW_ATTN_MMA", "1") != "0"
 
 
 class ConvWindowAttention(Mixer):
@@ -103,21 +110,33 @@ class ConvWindowAttention(Mixer):
         out = workspace.empty((T, nh * vd), x.dtype, x.device)
         # no query reads more keys than the window and the kept first ones: no more key slices than those fill
         reach = self.window + self.keep_first if self.window else 0
-        plan = ctx.plan(("attention", nh, nkv, "plain", reach),
-                        lambda: AttentionPlan(ctx, nh, nkv, DECODE_ROWS, SPAN_ROWS, max_keys=reach))
+        # bfloat16 with keys and values of 64 or 128 lanes: the tensor-core kernel; else the plain one
+        mma = MMA_ATTENTION and vd == hd and kv.pages.dim() == 5 and ops.attn_mma_supported(x.dtype, hd)
+        dec_rows, span_rows = (MMA_DECODE_ROWS, MMA_SPAN_ROWS) if mma else (DECODE_ROWS, SPAN_ROWS)
+        clustered = hd if mma and CLUSTER_MERGE and torch.cuda.is_available() else None
+        plan = ctx.plan(("attention", nh, nkv, mma, clustered, reach),
+                        lambda: AttentionPlan(ctx, nh, nkv, dec_rows, span_rows, clustered, max_keys=reach))
         common = dict(nh=nh, nkv=nkv, hd=hd, window=self.window, status=ctx.status, table_row=ctx.slots, scale=self.scale,
-                      keep_first=self.keep_first, dist_a=self.dist_a, dist_b=self.dist_b, hd_v=vd)
+                      keep_first=self.keep_first, dist_a=self.dist_a, dist_b=self.dist_b)
+        args = (q, out, kv.pages, group.block_table, ctx.q_start, ctx.q_len, ctx.ctx_len)
         if plan.n_dec:
             S = plan.nslices
+            cluster = plan.cluster if mma else 0
             part_o = part_ml = None
-            if S > 1:
+            if S > 1 and not cluster:
                 part_o = workspace.empty((plan.n_dec * nh * S, vd), torch.float32, x.device)
                 part_ml = workspace.empty((plan.n_dec * nh * S, 2), torch.float32, x.device)
-            ops.attn_window_bias(q, out, kv.pages, group.block_table, ctx.q_start, ctx.q_len, ctx.ctx_len, plan.dec_items,
-                                 plan.n_dec * S, DECODE_ROWS, part_o, part_ml, **common)
-            if S > 1:
-                ops.attn_merge(part_o, part_ml, plan.dec_rows, out, plan.n_dec, nh, vd, S)
+            if mma:
+                ops.attn_mma(*args, plan.dec_items, plan.n_dec * S, dec_rows, part_o, part_ml,
+                             slice_counters=plan.slice_counters if S > 1 else None, dec_rows=plan.dec_rows, cluster=cluster,
+                             **common)
+            else:
+                ops.attn_window_bias(*args, plan.dec_items, plan.n_dec * S, dec_rows, part_o, part_ml, hd_v=vd, **common)
+                if S > 1:
+                    ops.attn_merge(part_o, part_ml, plan.dec_rows, out, plan.n_dec, nh, vd, S)
         if plan.n_span_items:
-            ops.attn_window_bias(q, out, kv.pages, group.block_table, ctx.q_start, ctx.q_len, ctx.ctx_len, plan.span_items,
-                                 plan.n_span_items, SPAN_ROWS, None, None, **common)
+            if mma:
+                ops.attn_mma(*args, plan.span_items, plan.n_span_items, span_rows, None, None, **common)
+            else:
+                ops.attn_window_bias(*args, plan.span_items, plan.n_span_items, span_rows, None, None, hd_v=vd, **common)
         return matmul_tn(out, self.w_o, ctx.status, out_dtype=torch.float32, allow_partials=True)
