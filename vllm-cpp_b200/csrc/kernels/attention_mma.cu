@@ -519,14 +519,14 @@ __global__ __launch_bounds__(WR * WK * 32 + (TMA ? 32 : 0)) void attn_mma_kernel
         ok_a[mr] = r_a[mr] < R;
         ok_b[mr] = r_a[mr] + 8 < R;
     }
-    float da_a[MR], db_a[MR], da_b[MR], db_b[MR];   // the distance penalty's a_h, b_h of rows a and b
+    float da_a[MR], db_a[MR], da_b[MR], db_b[MR];   // the distance penalty's a_h ln 2 and b_h of rows a and b
 #pragma unroll
     for (int mr = 0; mr < MR; ++mr) {
         const bool on = a.dist_a != nullptr;
         const int ha = head0 + r_a[mr] % gq, hb = head0 + (r_a[mr] + 8) % gq;
-        da_a[mr] = on && ok_a[mr] ? a.dist_a[ha] : 0.f;
+        da_a[mr] = on && ok_a[mr] ? a.dist_a[ha] * 0.6931471805599453f : 0.f;     // a ln 2: the logarithm is taken to base 2
         db_a[mr] = on && ok_a[mr] ? a.dist_b[ha] : 0.f;
-        da_b[mr] = on && ok_b[mr] ? a.dist_a[hb] : 0.f;
+        da_b[mr] = on && ok_b[mr] ? a.dist_a[hb] * 0.6931471805599453f : 0.f;
         db_b[mr] = on && ok_b[mr] ? a.dist_b[hb] : 0.f;
     }
 
@@ -601,20 +601,38 @@ __global__ __launch_bounds__(WR * WK * 32 + (TMA ? 32 : 0)) void attn_mma_kernel
             }
             // mask (only where the tile touches an edge of some row's key range), running maximum
             // rows beyond R hold zero queries and are never written, so they need no mask of their own
-            const bool inner = a.dist_a == nullptr && key0 >= kb && key0 + KW <= ke && key0 + KW - 1 <= pos0 &&
+            const bool inner = key0 >= kb && key0 + KW <= ke && key0 + KW - 1 <= pos0 &&
                                (W <= 0 || key0 > pos_last - W || key0 + KW <= KF);
+            const bool penal = a.dist_a != nullptr;
+            const int kq = key0 + 2 * (lane & 3);   // this thread's first key of the tile
             const bool all_inner = __all_sync(0xffffffffu, inner);
             uint32_t pa[MR][KW / 16][4];
 #pragma unroll
             for (int mr = 0; mr < MR; ++mr) {
                 float mx_a = -CUDART_INF_F, mx_b = -CUDART_INF_F;
-                if (all_inner) {
+                // the distance penalty a ln(1 + b (pos - key)) = (a ln 2) log2((1 + b (pos - kq)) - b k) for the thread's
+                // k-th key: one multiply-add, one base-2 logarithm and one multiply-add a score (the fast logarithm's
+                // error, some 1e-6, is far below the rounding of the bfloat16 operands)
+                const float one_a = fmaf(db_a[mr], (float)(pos_a[mr] - kq), 1.f), one_b = fmaf(db_b[mr], (float)(pos_b[mr] - kq), 1.f);
+                if (all_inner && !penal) {
 #pragma unroll
                     for (int i = 0; i < NS; ++i) {
 #pragma unroll
                         for (int c = 0; c < 2; ++c) {
                             s[mr][i][c] *= a.scale;
                             s[mr][i][2 + c] *= a.scale;
+                            mx_a = fmaxf(mx_a, s[mr][i][c]);
+                            mx_b = fmaxf(mx_b, s[mr][i][2 + c]);
+                        }
+                    }
+                } else if (all_inner) {
+#pragma unroll
+                    for (int i = 0; i < NS; ++i) {
+#pragma unroll
+                        for (int c = 0; c < 2; ++c) {
+                            const float k = (float)(i * 8 + c);
+                            s[mr][i][c] = fmaf(-da_a[mr], __log2f(fmaf(-db_a[mr], k, one_a)), s[mr][i][c] * a.scale);
+                            s[mr][i][2 + c] = fmaf(-da_b[mr], __log2f(fmaf(-db_b[mr], k, one_b)), s[mr][i][2 + c] * a.scale);
                             mx_a = fmaxf(mx_a, s[mr][i][c]);
                             mx_b = fmaxf(mx_b, s[mr][i][2 + c]);
                         }
@@ -629,11 +647,10 @@ __global__ __launch_bounds__(WR * WK * 32 + (TMA ? 32 : 0)) void attn_mma_kernel
                             const bool sa = ok_a[mr] && in && kidx <= pos_a[mr] && (W <= 0 || kidx > pos_a[mr] - W || kidx < KF);
                             const bool sb = ok_b[mr] && in && kidx <= pos_b[mr] && (W <= 0 || kidx > pos_b[mr] - W || kidx < KF);
                             float va = s[mr][i][c] * a.scale, vb = s[mr][i][2 + c] * a.scale;
-                            if (a.dist_a != nullptr) {
-                                // the penalty of the distance (ln through the fast base-2 logarithm: its error, some 1e-6,
-                                // is far below the rounding of the bfloat16 operands)
-                                if (sa) va -= da_a[mr] * __logf(fmaf(db_a[mr], (float)(pos_a[mr] - kidx), 1.f));
-                                if (sb) vb -= da_b[mr] * __logf(fmaf(db_b[mr], (float)(pos_b[mr] - kidx), 1.f));
+                            if (penal) {
+                                const float k = (float)(i * 8 + c);
+                                if (sa) va = fmaf(-da_a[mr], __log2f(fmaf(-db_a[mr], k, one_a)), va);
+                                if (sb) vb = fmaf(-da_b[mr], __log2f(fmaf(-db_b[mr], k, one_b)), vb);
                             }
                             s[mr][i][c] = sa ? va : -CUDART_INF_F;
                             s[mr][i][2 + c] = sb ? vb : -CUDART_INF_F;

@@ -49,6 +49,52 @@ __device__ __forceinline__ float rows_at(const RowsIn& in, long long t, int c) {
     return v;
 }
 
+// the same for four neighbouring channels at once (c a multiple of 4, every stride and base a multiple of 4 elements)
+__device__ __forceinline__ float4 rows_at4(const RowsIn& in, long long t, int c) {
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float* p = in.p + t * in.ld + c;
+    for (int s = 0; s < in.S; ++s) {
+        const float4 a = *reinterpret_cast<const float4*>(p + (long long)s * in.s_stride);
+        v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+    }
+    if (in.bias != nullptr) {
+        const float4 b = *reinterpret_cast<const float4*>(in.bias + c);
+        v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+    }
+    return v;
+}
+
+__device__ __forceinline__ float4 conv_at4(const RowsIn& in, const float* __restrict__ w, const float* __restrict__ st, int C,
+                                           int taps, long long t, int rel, int c) {
+    float4 y = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int j = 0; j < taps; ++j) {
+        const int back = taps - 1 - j;
+        const float4 u = rel - back >= 0 ? rows_at4(in, t - back, c) : *reinterpret_cast<const float4*>(st + (long long)(rel + j) * C + c);
+        const float* wc = w + (long long)c * taps + j;
+        y.x = fmaf(wc[0], u.x, y.x);
+        y.y = fmaf(wc[taps], u.y, y.y);
+        y.z = fmaf(wc[2 * taps], u.z, y.z);
+        y.w = fmaf(wc[3 * taps], u.w, y.w);
+    }
+    return y;
+}
+
+template <typename T> __device__ __forceinline__ void store4(T* p, float4 v);
+template <> __device__ __forceinline__ void store4<float>(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* p, float4 v) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 u;
+    u.x = *reinterpret_cast<const uint32_t*>(&a);
+    u.y = *reinterpret_cast<const uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(p) = u;
+}
+
+// whether rows can be read four channels at a time
+inline bool rows_vec_ok(const RowsIn& r) {
+    return r.p == nullptr || (((uintptr_t)r.p % 16 == 0) && r.ld % 4 == 0 && (r.S <= 1 || r.s_stride % 4 == 0) &&
+                              (r.bias == nullptr || (uintptr_t)r.bias % 16 == 0));
+}
+
 // sum_j w[c][j] * u(rel - taps + 1 + j) for the row at place `rel` of its entry (row index t); places before the
 // entry's first row come from the state row st[k][c], k = place + taps - 1
 __device__ __forceinline__ float conv_at(const RowsIn& in, const float* __restrict__ w, const float* __restrict__ st, int C,
@@ -99,6 +145,29 @@ __global__ void causal_conv_kernel(RowsIn in, const float* __restrict__ w, const
         float y = taps > 0 ? conv_at(in, w, state + (long long)slots[e] * slot_stride, C, taps, t, t - q_start[e], c) : 0.f;
         if (add_input) y += u;
         out_conv[(size_t)t * C + c] = from_f32<TOUT>(y);
+    }
+}
+
+// four channels a thread
+template <typename TOUT>
+__global__ void causal_conv_vec_kernel(RowsIn in, const float* __restrict__ w, const float* __restrict__ state,
+                                       long long slot_stride, const int* __restrict__ q_start, const int* __restrict__ q_len,
+                                       const int* __restrict__ slots, int E, int T, int C, int taps, int add_input,
+                                       TOUT* __restrict__ out_conv, TOUT* __restrict__ out_copy) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.y;
+    const int c = 4 * (blockIdx.x * blockDim.x + threadIdx.x);
+    if (c >= C) return;
+    const int e = entry_of_row(q_start, q_len, E, t);
+    if (e < 0) return;
+    const float4 u = rows_at4(in, t, c);
+    if (out_copy != nullptr) store4<TOUT>(out_copy + (size_t)t * C + c, u);
+    if (out_conv != nullptr) {
+        float4 y = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (taps > 0) y = conv_at4(in, w, state + (long long)slots[e] * slot_stride, C, taps, t, t - q_start[e], c);
+        if (add_input) { y.x += u.x; y.y += u.y; y.z += u.z; y.w += u.w; }
+        store4<TOUT>(out_conv + (size_t)t * C + c, y);
     }
 }
 
@@ -157,14 +226,15 @@ struct QkvArgs {
 };
 
 // a block a row; its warps take the heads in turn (query heads, then key heads, then value heads)
-template <typename TOUT>
+template <typename TOUT, bool VEC>
 __global__ __launch_bounds__(256) void qkv_conv_norm_store_kernel(QkvArgs a) {
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x;
     const int e = entry_of_row(a.q_start, a.q_len, a.E, t);
     if (e < 0) return;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const int lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    const int warp = (threadIdx.x >> 5) + blockIdx.y * nwarps;     // the head this warp takes
     const int rel = t - a.q_start[e];
     const float* st = a.state != nullptr ? a.state + (long long)a.slots[e] * a.slot_stride : nullptr;
     const int units = a.nh + (a.has_kv ? 2 * a.nkv : 0);
@@ -179,7 +249,50 @@ __global__ __launch_bounds__(256) void qkv_conv_norm_store_kernel(QkvArgs a) {
     TOUT* q_out = reinterpret_cast<TOUT*>(a.q_out);
     TOUT* pages = reinterpret_cast<TOUT*>(a.pages);
     constexpr int PER = VCB_MAX_HEAD_DIM / 32;
-    for (int u = warp; u < units; u += nwarps) {
+    if (VEC) {
+        // four neighbouring lanes of the head a thread: 16-byte loads, 8- or 16-byte stores
+        constexpr int PER4 = VCB_MAX_HEAD_DIM / 128;
+        const int u = warp;
+        if (u >= units) return;
+        int c0, n, kind;
+        if (u < a.nh) { kind = 0; n = a.hd; c0 = u * a.hd; }
+        else if (u < a.nh + a.nkv) { kind = 1; n = a.hd; c0 = a.nh * a.hd + (u - a.nh) * a.hd; }
+        else { kind = 2; n = a.hd_v; c0 = (a.nh + a.nkv) * a.hd + (u - a.nh - a.nkv) * a.hd_v; }
+        float4 y[PER4];
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < PER4; ++i) {
+            const int d = 4 * (lane + 32 * i);
+            y[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (d < n) {
+                y[i] = a.taps > 0 ? conv_at4(a.in, a.w, st, a.C, a.taps, t, rel, c0 + d) : rows_at4(a.in, t, c0 + d);
+                ss += y[i].x * y[i].x + y[i].y * y[i].y + y[i].z * y[i].z + y[i].w * y[i].w;
+            }
+        }
+        float mul = 1.f;
+        if (kind != 2 && a.use_norm) {
+            ss = warp_sum(ss);
+            mul = 1.f / sqrtf(ss / (float)n + a.eps);
+        }
+        TOUT* dst = nullptr;
+        if (kind == 0) dst = q_out + (size_t)t * a.nh * a.hd + c0;
+        else if (slot >= 0) {
+            const long long page = slot / a.page_size, off = slot % a.page_size;
+            const int kvh = kind == 1 ? u - a.nh : u - a.nh - a.nkv;
+            dst = pages + page * a.page_stride +
+                  (kind == 1 ? ((long long)kvh * a.page_size + off) * a.hd
+                             : (long long)a.nkv * a.page_size * a.hd + ((long long)kvh * a.page_size + off) * a.hd_v);
+        }
+        if (dst != nullptr) {
+#pragma unroll
+            for (int i = 0; i < PER4; ++i) {
+                const int d = 4 * (lane + 32 * i);
+                if (d < n) store4<TOUT>(dst + d, make_float4(y[i].x * mul, y[i].y * mul, y[i].z * mul, y[i].w * mul));
+            }
+        }
+        return;
+    }
+    for (int u = warp; u < units; u += nwarps * gridDim.y) {
         int c0, n, kind;   // kind 0: query, 1: key, 2: value
         if (u < a.nh) { kind = 0; n = a.hd; c0 = u * a.hd; }
         else if (u < a.nh + a.nkv) { kind = 1; n = a.hd; c0 = a.nh * a.hd + (u - a.nh) * a.hd; }
@@ -247,6 +360,76 @@ __global__ void gated_norm_add_kernel(float* __restrict__ resid, RowsIn y, RowsI
     }
 }
 
+// the same with four channels a thread and everything a thread needs held in registers: every load of the row is
+// asked for before the first result is needed
+template <typename TOUT, int VPT>
+__global__ __launch_bounds__(1024) void gated_norm_add_vec_kernel(float* __restrict__ resid, RowsIn y, RowsIn g,
+                                                                  const float* __restrict__ w, float eps,
+                                                                  const int* __restrict__ q_start, const int* __restrict__ q_len,
+                                                                  int E, int H, TOUT* __restrict__ out_cast) {
+    __shared__ float scratch[33];
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x;
+    if (entry_of_row(q_start, q_len, E, t) < 0) return;
+    const int nv = H >> 2;
+    float4 v[VPT], r[VPT], gs[VPT];
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int idx = threadIdx.x + i * blockDim.x;
+        if (idx < nv) {
+            r[i] = *reinterpret_cast<const float4*>(resid + (size_t)t * H + 4 * idx);
+            v[i] = rows_at4(y, t, 4 * idx);
+            if (g.p != nullptr) gs[i] = rows_at4(g, t, 4 * idx);
+        }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int idx = threadIdx.x + i * blockDim.x;
+        if (idx < nv) {
+            if (g.p != nullptr) {
+                v[i].x *= 1.f / (1.f + expf(-gs[i].x)); v[i].y *= 1.f / (1.f + expf(-gs[i].y));
+                v[i].z *= 1.f / (1.f + expf(-gs[i].z)); v[i].w *= 1.f / (1.f + expf(-gs[i].w));
+            }
+            ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+        }
+    }
+    ss = block_sum(ss, scratch);
+    const float mul = 1.f / sqrtf(ss / (float)H + eps);
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int idx = threadIdx.x + i * blockDim.x;
+        if (idx < nv) {
+            const float4 ww = *reinterpret_cast<const float4*>(w + 4 * idx);
+            float4 x = r[i];
+            x.x += v[i].x * mul * ww.x; x.y += v[i].y * mul * ww.y; x.z += v[i].z * mul * ww.z; x.w += v[i].w * mul * ww.w;
+            *reinterpret_cast<float4*>(resid + (size_t)t * H + 4 * idx) = x;
+            if (out_cast != nullptr) store4<TOUT>(out_cast + (size_t)t * H + 4 * idx, x);
+        }
+    }
+}
+
+template <typename TOUT>
+__global__ void bias_act_vec_kernel(RowsIn in, TOUT* __restrict__ out, long long total4, int C4, int kind) {
+    pdl_trigger();
+    pdl_wait();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total4; i += (long long)gridDim.x * blockDim.x) {
+        const long long t = i / C4;
+        const int c = 4 * (int)(i % C4);
+        float4 z = rows_at4(in, t, c);
+        float* f = reinterpret_cast<float*>(&z);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float x = f[k];
+            if (kind == 0) f[k] = 0.5f * x * (1.f + erff(x * 0.70710678118654752440f));
+            else if (kind == 1) f[k] = 0.5f * x * (1.f + tanhf(0.79788456080286535588f * (x + 0.044715f * x * x * x)));
+            else f[k] = x / (1.f + expf(-x));
+        }
+        store4<TOUT>(out + (size_t)t * (4 * (size_t)C4) + c, z);
+    }
+}
+
 template <typename TOUT>
 __global__ void bias_act_kernel(RowsIn in, TOUT* __restrict__ out, long long total, int C, int kind) {
     pdl_trigger();
@@ -284,6 +467,19 @@ VCB_API int vcb_causal_conv(const float* in, int S, long long s_stride, long lon
     VCB_CHECK_ARG(taps < 2 || state != nullptr, "causal_conv: a convolution over %d tokens needs the requests' state", taps);
     VCB_CHECK_ARG(T <= 65535, "causal_conv: %d rows in one step (at most 65535)", T);
     RowsIn r{in, S < 1 ? 1 : S, s_stride, ld, bias};
+    const bool vec = C % 4 == 0 && rows_vec_ok(r) && (uintptr_t)out_conv % 16 == 0 && (uintptr_t)out_copy % 16 == 0 &&
+                     (state == nullptr || ((uintptr_t)state % 16 == 0 && slot_stride % 4 == 0));
+    if (vec) {
+        const dim3 grid4((C / 4 + 127) / 128, T), block4(128);
+        if (out_dtype == VCB_F32)
+            launch_pdl(causal_conv_vec_kernel<float>, grid4, block4, 0, stream, r, w, state, slot_stride, q_start, q_len, slots, E, T,
+                       C, taps, add_input, (float*)out_conv, (float*)out_copy);
+        else
+            launch_pdl(causal_conv_vec_kernel<__nv_bfloat16>, grid4, block4, 0, stream, r, w, state, slot_stride, q_start, q_len,
+                       slots, E, T, C, taps, add_input, (__nv_bfloat16*)out_conv, (__nv_bfloat16*)out_copy);
+        VCB_CHECK_LAUNCH("causal_conv");
+        return 0;
+    }
     const dim3 grid((C + 255) / 256, T), block(256);
     if (out_dtype == VCB_F32)
         launch_pdl(causal_conv_kernel<float>, grid, block, 0, stream, r, w, state, slot_stride, q_start, q_len, slots, E, T, C,
@@ -328,9 +524,20 @@ VCB_API int vcb_qkv_conv_norm_store(const float* in, int S, long long s_stride, 
     a.q_out = q_out; a.pages = pages; a.page_stride = page_stride; a.page_size = page_size; a.num_pages = num_pages;
     a.has_kv = has_kv; a.status = status;
     const int units = nh + (has_kv ? 2 * nkv : 0);
-    const int threads = 32 * (units < 8 ? units : 8);
-    if (out_dtype == VCB_F32) launch_pdl(qkv_conv_norm_store_kernel<float>, dim3(T), dim3(threads), 0, stream, a);
-    else launch_pdl(qkv_conv_norm_store_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, a);
+    const int warps = units < 4 ? units : 4;
+    const dim3 grid(T, (units + warps - 1) / warps), block(32 * warps);
+    VCB_CHECK_ARG(grid.y <= 65535, "qkv_conv_norm_store: %d heads", units);
+    const size_t esz = out_dtype == VCB_F32 ? 4 : 2;
+    const bool vec = hd % 4 == 0 && hd_v % 4 == 0 && rows_vec_ok(a.in) && (state == nullptr || ((uintptr_t)state % 16 == 0 && slot_stride % 4 == 0)) &&
+                     (uintptr_t)q_out % 16 == 0 && (!has_kv || ((uintptr_t)pages % 16 == 0 && (page_stride * esz) % 16 == 0 &&
+                                                               ((long long)nkv * page_size * hd * esz) % 16 == 0));
+    if (out_dtype == VCB_F32) {
+        if (vec) launch_pdl(qkv_conv_norm_store_kernel<float, true>, grid, block, 0, stream, a);
+        else launch_pdl(qkv_conv_norm_store_kernel<float, false>, grid, block, 0, stream, a);
+    } else {
+        if (vec) launch_pdl(qkv_conv_norm_store_kernel<__nv_bfloat16, true>, grid, block, 0, stream, a);
+        else launch_pdl(qkv_conv_norm_store_kernel<__nv_bfloat16, false>, grid, block, 0, stream, a);
+    }
     VCB_CHECK_LAUNCH("qkv_conv_norm_store");
     return 0;
 }
@@ -344,6 +551,18 @@ VCB_API int vcb_gated_norm_add(float* resid, const float* y, int Sy, long long y
     if (T == 0) return 0;
     RowsIn ry{y, Sy < 1 ? 1 : Sy, y_stride, ldy, nullptr};
     RowsIn rg{g, Sg < 1 ? 1 : Sg, g_stride, ldg, gb};
+    if (H % 4 == 0 && H / 4 <= 4096 && rows_vec_ok(ry) && rows_vec_ok(rg) && (uintptr_t)resid % 16 == 0 && (uintptr_t)w % 16 == 0 &&
+        (uintptr_t)out_cast % 16 == 0) {
+        const int nv = H / 4;
+        const int vpt = nv <= 1024 ? 1 : (nv <= 2048 ? 2 : 4);
+        const int threads4 = ((nv + vpt - 1) / vpt + 31) / 32 * 32;
+#define VCB_GNA(TOUT, V) launch_pdl(gated_norm_add_vec_kernel<TOUT, V>, dim3(T), dim3(threads4), 0, stream, resid, ry, rg, w, eps, q_start, q_len, E, H, (TOUT*)out_cast)
+        if (out_dtype == VCB_F32) { if (vpt == 1) VCB_GNA(float, 1); else if (vpt == 2) VCB_GNA(float, 2); else VCB_GNA(float, 4); }
+        else { if (vpt == 1) VCB_GNA(__nv_bfloat16, 1); else if (vpt == 2) VCB_GNA(__nv_bfloat16, 2); else VCB_GNA(__nv_bfloat16, 4); }
+#undef VCB_GNA
+        VCB_CHECK_LAUNCH("gated_norm_add");
+        return 0;
+    }
     const size_t smem = ((size_t)H + 64) * sizeof(float);
     const int threads = H >= 1024 ? 1024 : (H >= 512 ? 512 : 256);
     if (out_dtype == VCB_F32) {
@@ -368,6 +587,14 @@ VCB_API int vcb_bias_act(const float* in, int S, long long s_stride, long long l
     VCB_CHECK_ARG(kind >= 0 && kind <= 2, "bias_act: unknown activation %d", kind);
     RowsIn r{in, S < 1 ? 1 : S, s_stride, ld, bias};
     const long long total = (long long)T * C;
+    if (C % 4 == 0 && rows_vec_ok(r) && (uintptr_t)out % 16 == 0) {
+        const long long total4 = total / 4;
+        const int blocks4 = (int)((total4 + 255) / 256 < 148 * 16 ? (total4 + 255) / 256 : 148 * 16);
+        if (out_dtype == VCB_F32) launch_pdl(bias_act_vec_kernel<float>, dim3(blocks4), dim3(256), 0, stream, r, (float*)out, total4, C / 4, kind);
+        else launch_pdl(bias_act_vec_kernel<__nv_bfloat16>, dim3(blocks4), dim3(256), 0, stream, r, (__nv_bfloat16*)out, total4, C / 4, kind);
+        VCB_CHECK_LAUNCH("bias_act");
+        return 0;
+    }
     const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
     if (out_dtype == VCB_F32) launch_pdl(bias_act_kernel<float>, dim3(blocks), dim3(256), 0, stream, r, (float*)out, total, C, kind);
     else launch_pdl(bias_act_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, r, (__nv_bfloat16*)out, total, C, kind);

@@ -39,6 +39,7 @@ class GatedPostNormBlock(Block):
         self.gate_w = [None, None]
         self.gate_b = [None, None]
         self.norm_w = [None, None]
+        self.gate_in_ff = False
 
     # ---- weights ----
     def tensor_specs(self):
@@ -61,6 +62,11 @@ class GatedPostNormBlock(Block):
                 self.gate_w[i] = store.matrix(p + n)
                 self.gate_b[i] = store.vector(p + n + ".b").float().contiguous()
             self.norm_w[i] = self.parts[norm].weight.float().contiguous()
+        # the feed-forward's gate reads what the feed-forward reads: one product for both where the part offers it
+        self.gate_in_ff = self.gated and self.has_ff and hasattr(self.parts["feed_forward"], "attach_side_rows")
+        if self.gate_in_ff:
+            self.parts["feed_forward"].attach_side_rows(self.gate_w[1])
+            self.gate_w[1] = None
 
     # ---- per-request state ----
     def _own_spec(self):
@@ -84,8 +90,9 @@ class GatedPostNormBlock(Block):
         return mine, (views if isinstance(theirs, tuple) else (views[0] if views else None))
 
     # ---- one step ----
-    def _sublayer_add(self, i, resid, delta, h, ctx, out_cast=None):
-        gate = matmul_tn(h, self.gate_w[i], ctx.status, out_dtype=torch.float32, allow_partials=True) if self.gated else None
+    def _sublayer_add(self, i, resid, delta, h, ctx, out_cast=None, gate=None):
+        if gate is None and self.gated:
+            gate = matmul_tn(h, self.gate_w[i], ctx.status, out_dtype=torch.float32, allow_partials=True)
         norm = self.parts["norm1" if i == 0 else "norm2"]
         ops.gated_norm_add(resid, delta, gate, self.gate_b[i], self.norm_w[i], norm.eps, ctx.q_start, ctx.q_len, ctx.E,
                            out_cast=out_cast)
@@ -119,7 +126,8 @@ class GatedPostNormBlock(Block):
         mark("mixer")
         if self.has_ff:
             h2 = resid if x2 is None else x2
-            d2 = self.parts["feed_forward"].forward(h2, ctx)
-            self._sublayer_add(1, resid, d2, h2, ctx)
+            ff = self.parts["feed_forward"]
+            d2 = ff.forward(h2, ctx)
+            self._sublayer_add(1, resid, d2, h2, ctx, gate=ff.side if self.gate_in_ff else None)
             mark("feed_forward")
         return None

@@ -76,6 +76,8 @@ class DenseMLP(FeedForward):
         self.up_name = prefix + str(params.get("up_tensor", "up_proj.weight"))
         self.down_name = prefix + str(params.get("down_tensor", "down_proj.weight"))
         self.w_up = self.w_down = None
+        self.side_rows = 0
+        self.side = None
 
     def tensor_specs(self):
         return [TensorSpec(self.up_name, (self.inter, self.hidden)), TensorSpec(self.down_name, (self.hidden, self.inter))]
@@ -84,8 +86,18 @@ class DenseMLP(FeedForward):
         self.w_up = store.matrix(self.up_name)
         self.w_down = store.matrix(self.down_name)
 
+    def attach_side_rows(self, weight) -> None:
+        """Stacks ``weight`` [rows, hidden] under the up projection (after ``bind``): whoever else multiplies the part's
+        input by a matrix gets its sums from the same product.  After ``forward`` they are in ``self.side``
+        ([T, rows] or [S, T, rows] partial sums, 32-bit, a view)."""
+        self.w_up = torch.cat([self.w_up, weight.to(self.w_up.dtype)], dim=0).contiguous()
+        self.side_rows = int(weight.shape[0])
+
     def forward(self, x, ctx):
         u = matmul_tn(x, self.w_up, ctx.status, out_dtype=torch.float32, allow_partials=True)
+        if self.side_rows:
+            self.side = u[..., self.inter:]
+            u = u[..., :self.inter]
         act = workspace.empty((x.shape[0], self.inter), x.dtype, x.device)
         ops.bias_act(u, act, self.activation)
         return matmul_tn(act, self.w_down, ctx.status, out_dtype=torch.float32, allow_partials=True, after_small_kernel=True)
