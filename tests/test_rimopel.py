@@ -37,10 +37,21 @@ def configs():
         "S": (RimopelConfig(vocab=260, width=128, norm_eps=1e-5, canon_taps=4, layers=(
             L("attention", mixer(4, 2, 64, 32, 0.15, conv=2, window=48, keep=2), "dense", 192),
             L("attention", mixer(2, 2, 32, 64, 0.2, conv=3, window=70, keep=17)))), 16),
+        # a width that is no multiple of 4 (rows the tensor-core product cannot address), five taps, eight taps on the
+        # mixer's input, as many KV heads as query heads; pages of 4
+        "U": (RimopelConfig(vocab=97, width=50, norm_eps=1e-4, canon_taps=8, layers=(
+            L("attention", mixer(5, 5, 6, 10, 0.4, conv=5, window=9, keep=2), "dense", 33),
+            L("attention", mixer(1, 1, 36, 4, 0.1, conv=2, window=30, keep=30), "dense", 7))), 4),
+        # an inner size below one k-block of the products, forty query heads on one KV head (more than a block of the
+        # plain attention kernel holds), a window of one key; pages of 8
+        "V": (RimopelConfig(vocab=128, width=40, norm_eps=1e-5, canon_taps=3, layers=(
+            L("attention", mixer(40, 1, 12, 12, 0.3, conv=3, window=1, keep=1), "dense", 24),
+            L("attention", mixer(8, 2, 16, 8, 0.25, conv=3, window=21, keep=4)))), 8),
     }
 
 
-LENGTHS = {"P": [40, 75, 128, 33, 90, 64, 17, 2], "Q": [1, 7, 33, 64, 150, 97, 130, 3], "S": [200, 65, 256, 3, 129, 64, 48, 100]}
+LENGTHS = {"P": [40, 75, 128, 33, 90, 64, 17, 2], "Q": [1, 7, 33, 64, 150, 97, 130, 3], "S": [200, 65, 256, 3, 129, 64, 48, 100],
+           "U": [50, 3, 77, 120, 9, 31], "V": [90, 2, 41, 70, 1, 33]}
 REL_TOL = {"float32": 2e-5, "bfloat16": 3e-2}
 
 
@@ -535,6 +546,17 @@ def test_replay(name, dtype, mode, rimopel_dirs, oracle, tmp_path):
     out = R.run_trace(rimopel_dirs[name], dtype, trace, tmp_path / "out", configs()[name][1], extra_args=["--poison"])
     worst = compare(name, dtype, trace, out, requests, oracle)
     print(f"{name} {dtype} {mode}: worst relative error {worst:.3e}, pool {trace.max_tokens} tokens, {len(trace.steps)} steps")
+
+
+@gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["U", "V"])
+@pytest.mark.parametrize("mode", ["tail", "mixed", "mixed_last"])
+def test_replay_of_awkward_sizes(name, dtype, mode, rimopel_dirs, oracle, tmp_path):
+    requests = requests_of(name)
+    trace = {"tail": R.tail_one_by_one, "mixed": R.mixed, "mixed_last": R.mixed_last}[mode](requests)
+    out = R.run_trace(rimopel_dirs[name], dtype, trace, tmp_path / "out", configs()[name][1], extra_args=["--poison"])
+    compare(name, dtype, trace, out, requests, oracle)
 
 
 @gpu
