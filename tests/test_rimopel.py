@@ -374,6 +374,8 @@ def run_window_attention(dtype, nh, nkv, d, dv, ps, window, keep, shapes, craft=
     if d == dv and ops.attn_mma_supported(dtype, d):
         for kernel in ("mma", "mma_no_tma", "mma_cluster"):
             plan = _run_window_attention(dtype, nh, nkv, d, dv, ps, window, keep, shapes, craft, penalty, scale, kernel)
+        if ops.attn_tc_supported(dtype, d, ps):
+            plan = _run_window_attention(dtype, nh, nkv, d, dv, ps, window, keep, shapes, craft, penalty, scale, "tc")   # tcgen05 for the prompt portions
     return plan
 
 
@@ -444,7 +446,9 @@ def _run_window_attention(dtype, nh, nkv, d, dv, ps, window, keep, shapes, craft
             slice_counters=plan.slice_counters if S > 1 else None, dec_rows=plan.dec_rows, cluster=cluster)
         if S > 1 and not mma:
             ops.attn_merge(po, pm, plan.dec_rows, out, plan.n_dec, nh, dv, S)
-    if plan.n_span_items:
+    if plan.n_span_items and kernel == "tc":
+        ops.attn_tc(q_flat, out, *args, plan.span_items, plan.n_span_items, nh, nkv, d, window, status, **opts)
+    elif plan.n_span_items:
         run(q_flat, out, *args, plan.span_items, plan.n_span_items, SPAN, None, None, nh, nkv, d, window, status)
     torch.cuda.synchronize()
     assert status.item() == 0
@@ -464,7 +468,7 @@ def _run_window_attention(dtype, nh, nkv, d, dv, ps, window, keep, shapes, craft
 @gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("nh,nkv,d,dv,ps", [(4, 2, 16, 24, 4), (3, 3, 20, 12, 8), (8, 2, 64, 64, 16), (2, 1, 128, 32, 16), (40, 1, 8, 256, 5),
-                                            (4, 1, 128, 128, 8), (6, 3, 64, 64, 5)])
+                                            (4, 1, 128, 128, 8), (6, 3, 64, 64, 5), (8, 2, 128, 128, 64), (4, 4, 64, 64, 32)])
 def test_window_attention_mixed_batch(dtype, nh, nkv, d, dv, ps):
     """Decoded tokens beside prompt portions: at the very start, before the window is full, far beyond it."""
     shapes = [(0, 1), (0, 7), (3, 1), (11, 1), (30, 2), (64, 33), (300, 1), (250, 70), (1, 2)]

@@ -69,6 +69,12 @@ struct TcArgs {
     int* status;
     int n_units;   // items x KV heads x chunks of the query heads that share one
     int* work;     // two counters, zero between launches: units handed out after the first of each block; blocks done
+    // Options of other designs (off: 0, null).  With a window, the first keep_first keys of a request stay visible to
+    // every later query: those that lie before a unit's window are key tiles of their own, ahead of the window's.
+    // dist_a, dist_b [nh]: a_h ln(1 + b_h (pos - j)) is taken off the score of key j.
+    int keep_first;
+    const float* dist_a;
+    const float* dist_b;
 };
 
 // a box of whole groups of 8 tokens, all lanes: coordinates (lane 0, token 0, half 0, group)
@@ -183,7 +189,15 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // chunk of the query heads that share it.
 struct Unit {
     int nq, kvh, head0, gq, R, row0, pos0, pos_last, k_end, pb_lo, pb_hi, t_first, n_tiles, bt_row;
+    int lo, n_first, n_ft;   // first key of the window; kept first keys before it, and the tiles (0 .. n_ft - 1) that hold them
 };
+// where tile `it` of a unit lies: its first key, the end of the keys that count, its first page and the end of its pages
+__device__ __forceinline__ int tile_k0(const Unit& u, int it) { return it < u.n_ft ? it * BNK : u.t_first + (it - u.n_ft) * BNK; }
+__device__ __forceinline__ int tile_kend(const Unit& u, int it) { return it < u.n_ft ? u.n_first : u.k_end; }
+__device__ __forceinline__ int tile_pb0(const Unit& u, int it, int pages_per_tile) {
+    return it < u.n_ft ? it * pages_per_tile : u.pb_lo + (it - u.n_ft) * pages_per_tile;
+}
+__device__ __forceinline__ int tile_pb_hi(const Unit& u, int it, int ps) { return it < u.n_ft ? (u.n_first + ps - 1) / ps : u.pb_hi; }
 constexpr int UNIT_INTS = sizeof(Unit) / sizeof(int);
 
 template <int HD, int KS, int VS>
@@ -229,7 +243,10 @@ __device__ __forceinline__ bool read_unit(const TcArgs& a, int unit, Unit& u) {
     u.pb_lo = lo / ps;
     u.pb_hi = (u.k_end + ps - 1) / ps;
     u.t_first = u.pb_lo * ps;     // tiles start on a page boundary: whole pages are loaded
-    u.n_tiles = (u.k_end - u.t_first + BNK - 1) / BNK;   // >= 1: every query sees itself
+    u.lo = lo;
+    u.n_first = a.window > 0 ? min(a.keep_first, lo) : 0;
+    u.n_ft = (u.n_first + BNK - 1) / BNK;
+    u.n_tiles = u.n_ft + (u.k_end - u.t_first + BNK - 1) / BNK;   // >= 1: every query sees itself
     u.bt_row = a.table_row ? a.table_row[e] : e;
     return true;
 }
@@ -246,7 +263,8 @@ __device__ __forceinline__ bool read_unit(const TcArgs& a, int unit, Unit& u) {
 // cannot be more than the K ring and the two score buffers ahead of them.
 // Barrier phases, ring stages and score buffers go on counting from unit to unit, so `t0` below is the number of
 // tiles of the units before.
-template <int HD, int KS, int VS>
+// OPT: built with the options of TcArgs (kept first keys, distance penalty); without, they cost nothing
+template <int HD, int KS, int VS, bool OPT>
 __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_constant__ CUtensorMap kv_map, TcArgs a) {
     using L = Layout<HD, KS, VS>;
     constexpr int CH = HD / 8;          // 16-byte chunks per row of head_dim
@@ -357,8 +375,8 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
         bool has = read_unit(a, unit, u);
         // this lane's page id for the first tile of the unit (see page_of below)
         auto first_page = [&](const Unit& w) {
-            const int pb = w.pb_lo + pl;
-            return (lane < 16 && pl < pages_per_tile && pb < w.pb_hi) ? a.block_table[(size_t)w.bt_row * a.max_blocks + pb] : -1;
+            const int pb = tile_pb0(w, 0, pages_per_tile) + pl;
+            return (lane < 16 && pl < pages_per_tile && pb < tile_pb_hi(w, 0, ps)) ? a.block_table[(size_t)w.bt_row * a.max_blocks + pb] : -1;
         };
         int next_page = has ? first_page(u) : -1;
         for (int seq = 0; unit >= 0 && ok; ++seq) {
@@ -408,8 +426,8 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
                 // about as long as a whole tile's products, and it stood between the stage's release and the load.
                 // Tiles of one kind are loaded in order, so the next tile is known.
                 auto page_of = [&](int it) {
-                    const int pb = u.pb_lo + it * pages_per_tile + pl;
-                    return (lane < 16 && it < u.n_tiles && pl < pages_per_tile && pb < u.pb_hi) ? bt[pb] : -1;
+                    const int pb = tile_pb0(u, it, pages_per_tile) + pl;
+                    return (lane < 16 && it < u.n_tiles && pl < pages_per_tile && pb < tile_pb_hi(u, it, ps)) ? bt[pb] : -1;
                 };
                 // loads K tile itk and V tile itv of the unit (either may be -1: none) once their stages are free;
                 // false: give up
@@ -429,7 +447,7 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
                     const bool mine = lane < 16 && it >= 0;
                     const int st = mine ? (t0 + it) % (copies_v ? VS : KS) : 0;
                     const uint32_t fullb = copies_v ? v_full(st) : k_full(st);
-                    const int np = mine ? min(pages_per_tile, u.pb_hi - (u.pb_lo + it * pages_per_tile)) : 0;
+                    const int np = mine ? min(pages_per_tile, tile_pb_hi(u, it, ps) - tile_pb0(u, it, pages_per_tile)) : 0;
                     if (mine && pl == 0) mbar_expect_tx(fullb, (uint32_t)(np * ps * ROWB));
                     __syncwarp();
                     if (pl < np) {   // at most 8 pages a tile: one box a lane
@@ -572,6 +590,11 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
             const int iq = r / u.gq, ih = r % u.gq;
             const int pos_r = u.pos0 + iq;
             const int lo_r = W > 0 ? max(0, pos_r - W + 1) : 0;
+            const int KF = OPT && W > 0 ? a.keep_first : 0;
+            // the distance penalty of the row's head, in the base-2 domain the weights are computed in: a log2(1 + b d)
+            const bool penal = OPT && a.dist_a != nullptr;
+            const float pen_a = penal && row_ok ? a.dist_a[u.head0 + ih] : 0.f, pen_b = penal && row_ok ? a.dist_b[u.head0 + ih] : 0.f;
+            const float sl2 = penal ? 1.f : scale_log2;   // what is left to multiply the scores by on their way to weights
 
             // The row's query -> shared memory (rows beyond R are zero).  The products of the unit before have all
             // been waited for (its last P . V, and with it everything issued earlier), so nothing reads the old rows.
@@ -587,7 +610,7 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
 
             for (int j = 0; j < u.n_tiles; ++j) {
                 const int gj = t0 + j, b = gj & 1, st = gj % VS;
-                const int k0 = u.t_first + j * BNK;
+                const int k0 = tile_k0(u, j), kend = tile_kend(u, j);
                 tl.mark(TL_ROW_ASKS, gj);
                 ok = mbar_wait(s_full(b), (gj >> 1) & 1, abort_flag, a.status);
                 if (!ok) break;
@@ -601,13 +624,23 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
                 tl.mark(TL_ROW_LOADED, gj);
 
                 // Scores stay unscaled in sv; only tiles that touch a row's own position or the window's edge mask.
-                const bool plain_tile = k0 + BNK - 1 <= u.pos0 && (W == 0 || k0 >= u.pos_last - W + 1);   // uniform over the block
+                // (a tile of kept first keys: every row sees all of it that counts)
+                const bool plain_tile = OPT && j < u.n_ft ? k0 + BNK <= kend
+                                                   : (k0 >= u.lo && k0 + BNK - 1 <= u.pos0 && (W == 0 || k0 >= u.pos_last - W + 1 || k0 + BNK <= KF));   // uniform over the block
                 float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+                if (penal) {
+                    // scaled scores less the penalty, times log2(e): one multiply-add, one logarithm, one multiply-add each
+                    const float one = fmaf(pen_b, (float)(pos_r - k0), 1.f);
+#pragma unroll
+                    for (int c = 0; c < BNK; ++c)
+                        sv[c / 16][c % 16] = __float_as_uint(fmaf(-pen_a, __log2f(fmaf(-pen_b, (float)c, one)), __uint_as_float(sv[c / 16][c % 16]) * scale_log2));
+                }
                 if (!plain_tile) {
+                    const int kbeg = OPT && j < u.n_ft ? 0 : u.lo;
 #pragma unroll
                     for (int c = 0; c < BNK; ++c) {
                         const int kidx = k0 + c;
-                        const bool valid = row_ok && kidx >= lo_r && kidx <= pos_r;
+                        const bool valid = row_ok && kidx >= kbeg && kidx < kend && kidx <= pos_r && (kidx >= lo_r || kidx < KF);
                         sv[c / 16][c % 16] = valid ? sv[c / 16][c % 16] : __float_as_uint(-CUDART_INF_F);
                     }
                 }
@@ -615,7 +648,7 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
                 for (int c = 0; c < BNK; c += 2)
                     mx4[(c >> 1) & 3] = max3(mx4[(c >> 1) & 3], __uint_as_float(sv[c / 16][c % 16]), __uint_as_float(sv[c / 16][c % 16 + 1]));
                 // the scale is positive: the maximum of the scaled scores is the scaled maximum
-                const float m_new = fmaxf(fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2, m_ref);
+                const float m_new = fmaxf(fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sl2, m_ref);
                 // Move the reference when the maximum has outgrown it.  O (in TMEM) holds the sum so far against the
                 // old reference: the warp rescales its 32 rows together, rows that keep theirs by a factor of one.
                 const bool first_keys = m_ref == -CUDART_INF_F && m_new != -CUDART_INF_F;   // nothing summed yet
@@ -645,7 +678,7 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
 
                 uint64_t sum4[4] = {0ull, 0ull, 0ull, 0ull};   // four pairs of partial sums, all +0
                 uint32_t pk[BNK / 2];
-                const uint64_t scale2 = pair_f32(scale_log2, scale_log2), shift2 = pair_f32(-m_sub, -m_sub);
+                const uint64_t scale2 = pair_f32(sl2, sl2), shift2 = pair_f32(-m_sub, -m_sub);
 #pragma unroll
                 for (int c = 0; c < BNK; c += 2) {
                     float x0, x1;
@@ -660,12 +693,12 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
                     l_run += lo4 + hi4;
                 }
 
-                if (k0 + BNK > u.k_end) {
+                if (k0 + BNK > kend) {
                     // The last page may hold slots beyond the sequence, and rows of pages that were not loaded are
                     // stale: their V must be finite, because a zero weight times NaN is NaN.
                     ok = mbar_wait(v_full(st), (gj / VS) & 1, abort_flag, a.status);
                     if (!ok) break;
-                    const int first = u.k_end - k0;
+                    const int first = kend - k0;
                     for (int idx = r; idx < (BNK - first) * CH; idx += ROWS) {
                         const int jj = first + idx / CH, c = idx % CH;
                         *reinterpret_cast<uint4*>(gen + L::V_OFF + st * L::KV_BYTES + swz_groups<HALVES>(jj, c)) = make_uint4(0, 0, 0, 0);
@@ -727,11 +760,11 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
     }
 }
 
-template <int HD>
+template <int HD, bool OPT>
 int launch(const CUtensorMap& map, const TcArgs& a, int n_items, cudaStream_t stream) {
     constexpr int KS = 3, VS = 2;
     using L = Layout<HD, KS, VS>;
-    auto kern = attn_tc_kernel<HD, KS, VS>;
+    auto kern = attn_tc_kernel<HD, KS, VS, OPT>;
     static bool opted = false;
     if (!opted) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
@@ -765,6 +798,12 @@ VCB_API int vcb_attn_tc_supported(int dtype, int hd, int page_size) {
            (page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64);
 }
 
+VCB_API int vcb_attn_tc_ex(const void* q, void* out, const void* pages, long long page_stride, const int* block_table,
+                           const int* table_row, int max_blocks, const int* q_start, const int* q_len, const int* ctx_len,
+                           const int* items, int n_items, int nh, int nkv, int hd, int page_size, int num_pages, int window,
+                           float scale, int keep_first, const float* dist_a, const float* dist_b, int* status, int* work,
+                           cudaStream_t stream);
+
 // Prompt portions only: every item has slice 0 of 1 and at most 128 rows (tokens x query heads per KV head).
 // work: two ints that are zero when the kernel starts and zero again when it ends (the blocks' queue of units); the
 // launches that share them must not overlap.
@@ -772,7 +811,17 @@ VCB_API int vcb_attn_tc(const void* q, void* out, const void* pages, long long p
                         const int* table_row, int max_blocks, const int* q_start, const int* q_len, const int* ctx_len,
                         const int* items, int n_items, int nh, int nkv, int hd, int page_size, int num_pages, int window,
                         float scale, int* status, int* work, cudaStream_t stream) {
+    return vcb_attn_tc_ex(q, out, pages, page_stride, block_table, table_row, max_blocks, q_start, q_len, ctx_len, items, n_items,
+                          nh, nkv, hd, page_size, num_pages, window, scale, 0, nullptr, nullptr, status, work, stream);
+}
+
+VCB_API int vcb_attn_tc_ex(const void* q, void* out, const void* pages, long long page_stride, const int* block_table,
+                           const int* table_row, int max_blocks, const int* q_start, const int* q_len, const int* ctx_len,
+                           const int* items, int n_items, int nh, int nkv, int hd, int page_size, int num_pages, int window,
+                           float scale, int keep_first, const float* dist_a, const float* dist_b, int* status, int* work,
+                           cudaStream_t stream) {
     if (n_items == 0) return 0;
+    VCB_CHECK_ARG(keep_first >= 0 && (dist_a == nullptr) == (dist_b == nullptr), "attn_tc: bad keep_first %d or half a distance penalty", keep_first);
     VCB_CHECK_ARG(nh > 0 && nkv > 0 && nh % nkv == 0, "attn_tc: %d query heads are not a multiple of %d KV heads", nh, nkv);
     VCB_CHECK_ARG(vcb_attn_tc_supported(VCB_BF16, hd, page_size), "attn_tc: head_dim %d with pages of %d tokens is not supported", hd, page_size);
     VCB_CHECK_ARG(window >= 0, "attn_tc: bad window %d", window);
@@ -786,6 +835,7 @@ VCB_API int vcb_attn_tc(const void* q, void* out, const void* pages, long long p
     const int g = nh / nkv;
     const int hchunks = (g + ROWS - 1) / ROWS;
     TcArgs a{(const __nv_bfloat16*)q, (__nv_bfloat16*)out, block_table, table_row, max_blocks, q_start, q_len, ctx_len,
-             items, nh, nkv, page_size, num_pages, window, scale, status, n_items * nkv * hchunks, work};
-    return hd == 64 ? launch<64>(map, a, n_items, stream) : launch<128>(map, a, n_items, stream);
+             items, nh, nkv, page_size, num_pages, window, scale, status, n_items * nkv * hchunks, work, keep_first, dist_a, dist_b};
+    if (keep_first > 0 || dist_a != nullptr) return hd == 64 ? launch<64, true>(map, a, n_items, stream) : launch<128, true>(map, a, n_items, stream);
+    return hd == 64 ? launch<64, false>(map, a, n_items, stream) : launch<128, false>(map, a, n_items, stream);
 }

@@ -87,6 +87,7 @@ def _declare(L):
         "vcb_attn_mma_decode_fused": [P, I, LL, P, P, I, I, F, P, I, P, P, P, LL, P, P, I, P, P, P, P, I, P, P, P, P, I, I,
                                       I, I, I, I, F, P, I, P],
         "vcb_attn_tc": [P, P, P, LL, P, P, I, P, P, P, P, I, I, I, I, I, I, I, F, P, P, P],
+        "vcb_attn_tc_ex": [P, P, P, LL, P, P, I, P, P, P, P, I, I, I, I, I, I, I, F, I, P, P, P, P, P],
         "vcb_attn_tc_supported": [I, I, I],
         "vcb_attn_stream": [P, P, P, LL, P, P, I, P, P, P, I, P, I, I, I, I, I, I, F, P, I, P],
         "vcb_attn_stream_supported": [I, I, I, I, I],
@@ -646,9 +647,10 @@ def attn_tc_supported(dtype: torch.dtype, hd: int, page_size: int) -> bool:
 
 
 def attn_tc(q, out, pages, block_table, q_start, q_len, ctx_len, items, n_items, nh, nkv, hd, window, status,
-            table_row=None, work=None):
+            table_row=None, work=None, scale=None, keep_first=0, dist_a=None, dist_b=None):
     """Attention of prompt portions on tcgen05 tensor cores (bfloat16, head_dim 64 or 128, pages of 8 to 64
-    tokens).  Items as for :func:`attn_paged` with one key slice and at most 128 rows each.  ``work``: two int32
+    tokens), with the options of :func:`attn_window_bias` (``scale``, ``keep_first``, ``dist_a``/``dist_b``).
+    Items as for :func:`attn_paged` with one key slice and at most 128 rows each.  ``work``: two int32
     zeros, zero again when the kernel is through (the queue its blocks take their units from); launches that share
     them must follow one another on a stream.  Made on the spot when not given."""
     if work is None:
@@ -660,9 +662,13 @@ def attn_tc(q, out, pages, block_table, q_start, q_len, ctx_len, items, n_items,
         _need(t, name, torch.int32)
     num_pages, two, nkv_p, page_size, hd_p = pages.shape
     assert two == 2 and nkv_p == nkv and hd_p == hd
-    _call("vcb_attn_tc", _p(q), _p(out), _p(pages), pages.stride(0), _p(block_table), _p(table_row),
+    if dist_a is not None:
+        _need(dist_a, "dist_a", torch.float32); _need(dist_b, "dist_b", torch.float32)
+        assert dist_a.numel() == nh and dist_b.numel() == nh
+    _call("vcb_attn_tc_ex", _p(q), _p(out), _p(pages), pages.stride(0), _p(block_table), _p(table_row),
           block_table.shape[1], _p(q_start), _p(q_len), _p(ctx_len), _p(items), n_items, nh, nkv, hd, page_size,
-          num_pages, int(window or 0), 1.0 / math.sqrt(hd), _p(status), _p(work), _stream())
+          num_pages, int(window or 0), 1.0 / math.sqrt(hd) if scale is None else float(scale), int(keep_first or 0),
+          _p(dist_a), _p(dist_b), _p(status), _p(work), _stream())
 
 
 def attn_mma(q, out, pages, block_table, q_start, q_len, ctx_len, items, n_items, rows_max, part_o, part_ml,

@@ -15,7 +15,8 @@ Per request the part keeps the keys and values in pages (given back as the windo
 kept first keys) and, for the convolution, the last taps - 1 rows of the stacked projection as a fixed-size state.
 Scores, softmax, the penalty, the norms and the convolution are 32-bit; keys, values and queries are stored in the
 compute dtype.  In bfloat16 with keys and values of 64 or 128 lanes the scores and the weighted sums run on the
-tensor cores (the kernel of the rotary attention part, with these options); otherwise on the plain kernel.
+tensor cores (the kernels of the rotary attention part, with these options: tcgen05 for prompt portions where the
+page size allows, mma.sync for decoded tokens); otherwise on the plain kernel.
 """
 from __future__ import annotations
 
@@ -25,7 +26,8 @@ import torch
 
 from .. import ops, workspace
 from ..weights.loader import TensorSpec
-from .attention import CLUSTER_MERGE, DECODE_ROWS, MMA_DECODE_ROWS, MMA_SPAN_ROWS, SPAN_ROWS, AttentionPlan
+from .attention import (CLUSTER_MERGE, DECODE_ROWS, MMA_DECODE_ROWS, MMA_SPAN_ROWS, SPAN_ROWS, TCGEN05_SPANS,
+                        AttentionPlan)
 from .base import CacheSpec, Mixer
 from .linear import matmul_tn
 
@@ -135,7 +137,9 @@ class ConvWindowAttention(Mixer):
                 if S > 1:
                     ops.attn_merge(part_o, part_ml, plan.dec_rows, out, plan.n_dec, nh, vd, S)
         if plan.n_span_items:
-            if mma:
+            if mma and TCGEN05_SPANS and ops.attn_tc_supported(x.dtype, hd, kv.pages.shape[3]):
+                ops.attn_tc(*args, plan.span_items, plan.n_span_items, work=plan.span_work, **common)
+            elif mma:
                 ops.attn_mma(*args, plan.span_items, plan.n_span_items, span_rows, None, None, **common)
             else:
                 ops.attn_window_bias(*args, plan.span_items, plan.n_span_items, span_rows, None, None, hd_v=vd, **common)
