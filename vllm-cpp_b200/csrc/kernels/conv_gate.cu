@@ -3,7 +3,9 @@
 //  * embed_sinusoid      x[t] = E[id_t] + s(p_t),  s(p)[2i] = sin(p f_i),  s(p)[2i+1] = cos(p f_i)
 //  * causal_conv         y_t = sum_j w[:, j] u_(t - taps + 1 + j)  per channel, u = 0 before a request's first token;
 //                        the taps - 1 inputs before a portion come from the request's state row
-//  * conv_state_update   the state row afterwards: the last taps - 1 inputs the request has seen
+//  * conv_state_update   the state row afterwards: the last taps - 1 inputs the request has seen (entries of one
+//                        token are brought up to date by the convolving kernel itself: a step of single tokens
+//                        launches no update)
 //  * qkv_conv_norm_store the same convolution on the stacked q, k, v projection (with its bias), then every query
 //                        and key head divided by its root mean square, queries to a buffer, keys and values to
 //                        the tokens' cache slots
@@ -108,6 +110,29 @@ __device__ __forceinline__ float conv_at(const RowsIn& in, const float* __restri
     return y;
 }
 
+// The state row of an entry that brought one token: its rows move up by one and the token's input is the last.  Done
+// by the thread that convolved the channel, after its own reads: with one token the entry has no other reader, so the
+// update needs no kernel of its own (conv_state_update leaves such entries out).
+__device__ __forceinline__ void state_push(float* __restrict__ st, int C, int taps, int c, float u) {
+    float old[MAX_TAPS];
+#pragma unroll
+    for (int k = 0; k < MAX_TAPS; ++k) old[k] = k + 1 < taps - 1 ? st[(long long)(k + 1) * C + c] : 0.f;
+#pragma unroll
+    for (int k = 0; k < MAX_TAPS; ++k)
+        if (k + 1 < taps - 1) st[(long long)k * C + c] = old[k];
+    st[(long long)(taps - 2) * C + c] = u;
+}
+__device__ __forceinline__ void state_push4(float* __restrict__ st, int C, int taps, int c, float4 u) {
+    float4 old[MAX_TAPS];
+#pragma unroll
+    for (int k = 0; k < MAX_TAPS; ++k)
+        old[k] = k + 1 < taps - 1 ? *reinterpret_cast<const float4*>(st + (long long)(k + 1) * C + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int k = 0; k < MAX_TAPS; ++k)
+        if (k + 1 < taps - 1) *reinterpret_cast<float4*>(st + (long long)k * C + c) = old[k];
+    *reinterpret_cast<float4*>(st + (long long)(taps - 2) * C + c) = u;
+}
+
 __global__ void embed_sinusoid_kernel(const void* __restrict__ table, int table_dtype, const int* __restrict__ ids,
                                       const int* __restrict__ positions, const float* __restrict__ inv_freq,
                                       float* __restrict__ out, int H, int V, int* __restrict__ status) {
@@ -128,7 +153,7 @@ __global__ void embed_sinusoid_kernel(const void* __restrict__ table, int table_
 }
 
 template <typename TOUT>
-__global__ void causal_conv_kernel(RowsIn in, const float* __restrict__ w, const float* __restrict__ state,
+__global__ void causal_conv_kernel(RowsIn in, const float* __restrict__ w, float* __restrict__ state,
                                    long long slot_stride, const int* __restrict__ q_start, const int* __restrict__ q_len,
                                    const int* __restrict__ slots, int E, int T, int C, int taps, int add_input,
                                    TOUT* __restrict__ out_conv, TOUT* __restrict__ out_copy) {
@@ -146,11 +171,12 @@ __global__ void causal_conv_kernel(RowsIn in, const float* __restrict__ w, const
         if (add_input) y += u;
         out_conv[(size_t)t * C + c] = from_f32<TOUT>(y);
     }
+    if (taps > 1 && q_len[e] == 1) state_push(state + (long long)slots[e] * slot_stride, C, taps, c, u);
 }
 
 // four channels a thread
 template <typename TOUT>
-__global__ void causal_conv_vec_kernel(RowsIn in, const float* __restrict__ w, const float* __restrict__ state,
+__global__ void causal_conv_vec_kernel(RowsIn in, const float* __restrict__ w, float* __restrict__ state,
                                        long long slot_stride, const int* __restrict__ q_start, const int* __restrict__ q_len,
                                        const int* __restrict__ slots, int E, int T, int C, int taps, int add_input,
                                        TOUT* __restrict__ out_conv, TOUT* __restrict__ out_copy) {
@@ -169,6 +195,7 @@ __global__ void causal_conv_vec_kernel(RowsIn in, const float* __restrict__ w, c
         if (add_input) { y.x += u.x; y.y += u.y; y.z += u.z; y.w += u.w; }
         store4<TOUT>(out_conv + (size_t)t * C + c, y);
     }
+    if (taps > 1 && q_len[e] == 1) state_push4(state + (long long)slots[e] * slot_stride, C, taps, c, u);
 }
 
 __global__ void conv_state_update_kernel(RowsIn in, float* __restrict__ state, long long slot_stride,
@@ -179,7 +206,7 @@ __global__ void conv_state_update_kernel(RowsIn in, float* __restrict__ state, l
     const int e = blockIdx.y;
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     const int n = q_len[e];
-    if (c >= C || n <= 0) return;
+    if (c >= C || n <= 1) return;    // (an entry of one token was brought up to date by the kernel that convolved it)
     float* st = state + (long long)slots[e] * slot_stride;
     const int keep = taps - 1;
     float old[MAX_TAPS];
@@ -207,7 +234,7 @@ __global__ void conv_state_update_kernel(RowsIn in, float* __restrict__ state, l
 struct QkvArgs {
     RowsIn in;
     const float* w;       // [C][taps] or null when taps == 0
-    const float* state;
+    float* state;
     long long slot_stride;
     const int* q_start;
     const int* q_len;
@@ -236,7 +263,8 @@ __global__ __launch_bounds__(256) void qkv_conv_norm_store_kernel(QkvArgs a) {
     const int lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
     const int warp = (threadIdx.x >> 5) + blockIdx.y * nwarps;     // the head this warp takes
     const int rel = t - a.q_start[e];
-    const float* st = a.state != nullptr ? a.state + (long long)a.slots[e] * a.slot_stride : nullptr;
+    float* st = a.state != nullptr ? a.state + (long long)a.slots[e] * a.slot_stride : nullptr;
+    const bool push = a.taps > 1 && a.q_len[e] == 1;   // one token: the state is brought up to date here
     const int units = a.nh + (a.has_kv ? 2 * a.nkv : 0);
     long long slot = -1;
     if (a.has_kv) {
@@ -266,6 +294,7 @@ __global__ __launch_bounds__(256) void qkv_conv_norm_store_kernel(QkvArgs a) {
             y[i] = make_float4(0.f, 0.f, 0.f, 0.f);
             if (d < n) {
                 y[i] = a.taps > 0 ? conv_at4(a.in, a.w, st, a.C, a.taps, t, rel, c0 + d) : rows_at4(a.in, t, c0 + d);
+                if (push) state_push4(st, a.C, a.taps, c0 + d, rows_at4(a.in, t, c0 + d));
                 ss += y[i].x * y[i].x + y[i].y * y[i].y + y[i].z * y[i].z + y[i].w * y[i].w;
             }
         }
@@ -305,6 +334,7 @@ __global__ __launch_bounds__(256) void qkv_conv_norm_store_kernel(QkvArgs a) {
             y[i] = 0.f;
             if (d < n) {
                 y[i] = a.taps > 0 ? conv_at(a.in, a.w, st, a.C, a.taps, t, rel, c0 + d) : rows_at(a.in, t, c0 + d);
+                if (push) state_push(st, a.C, a.taps, c0 + d, rows_at(a.in, t, c0 + d));
                 ss = fmaf(y[i], y[i], ss);
             }
         }
@@ -458,9 +488,10 @@ VCB_API int vcb_embed_sinusoid(const void* table, int table_dtype, const int* id
 }
 
 // in: [S][T][ld] 32-bit (+ bias); out_conv = conv(in) (+ in with add_input), out_copy = in, both [T][C] of out_dtype,
-// either may be null.  taps 0: no convolution (out_conv = in with add_input, else zeros).  state [slots][taps-1][C].
+// either may be null.  taps 0: no convolution (out_conv = in with add_input, else zeros).  state [slots][taps-1][C]:
+// read, and for entries of one token brought up to date as well (entries of more need vcb_conv_state_update afterwards).
 VCB_API int vcb_causal_conv(const float* in, int S, long long s_stride, long long ld, const float* bias, const float* w,
-                            const float* state, long long slot_stride, const int* q_start, const int* q_len,
+                            float* state, long long slot_stride, const int* q_start, const int* q_len,
                             const int* slots, int E, int T, int C, int taps, int add_input, void* out_conv,
                             void* out_copy, int out_dtype, cudaStream_t stream) {
     if (T == 0 || C == 0) return 0;
@@ -506,7 +537,7 @@ VCB_API int vcb_conv_state_update(const float* in, int S, long long s_stride, lo
 }
 
 VCB_API int vcb_qkv_conv_norm_store(const float* in, int S, long long s_stride, long long ld, const float* bias,
-                                    const float* w, const float* state, long long slot_stride, const int* q_start,
+                                    const float* w, float* state, long long slot_stride, const int* q_start,
                                     const int* q_len, const int* slots, const int* slot_map, int E, int T, int taps, int nh,
                                     int nkv, int hd, int hd_v, int use_norm, float eps, void* q_out, void* pages,
                                     long long page_stride, int page_size, int num_pages, int has_kv, int out_dtype,

@@ -437,7 +437,8 @@ def causal_conv(x, weight, state, q_start, q_len, slots, n_entries, out_conv=Non
     """Per channel, over the tokens of each entry: out_conv[t] = sum_j weight[:, j] x[t - taps + 1 + j] (+ x[t] with
     ``add_input``), the taps - 1 inputs before an entry's first row read from ``state`` [slots, taps - 1, C] (32-bit)
     at the entry's slot; out_copy[t] = x[t].  x: 32-bit [T, C] or [S, T, C] partial sums, ``bias`` [C] added.
-    ``weight`` None: no convolution.  Rows outside every entry are left alone."""
+    ``weight`` None: no convolution.  Rows outside every entry are left alone.  The state row of an entry that brought
+    one token is brought up to date as well; entries of more tokens need :func:`conv_state_update` afterwards."""
     S, ss, ld = _rows_in(x, "x")
     T, C = x.shape[-2:]
     taps = 0 if weight is None else weight.shape[1]
@@ -456,8 +457,9 @@ def causal_conv(x, weight, state, q_start, q_len, slots, n_entries, out_conv=Non
 
 
 def conv_state_update(x, state, q_start, q_len, slots, n_entries, bias=None):
-    """After :func:`causal_conv` (or :func:`qkv_conv_norm_store`): each entry's state row holds the last taps - 1
-    inputs its request has seen (older ones move up where the entry brought fewer)."""
+    """After :func:`causal_conv` (or :func:`qkv_conv_norm_store`): the state row of each entry of two tokens or more
+    holds the last taps - 1 inputs its request has seen (older ones move up where the entry brought fewer).  Entries of
+    one token were brought up to date by the convolving kernel."""
     S, ss, ld = _rows_in(x, "x")
     C = x.shape[-1]
     _need(state, "state", torch.float32)
@@ -472,7 +474,8 @@ def qkv_conv_norm_store(qkv, bias, weight, state, q_start, q_len, slots, slot_ma
     """The stacked q, k, v projection ``qkv`` (32-bit [T, C] or [S, T, C], C = nh hd + nkv (hd + hd_v)) with ``bias``
     [C]; a causal convolution per channel (``weight`` [C, taps] or None) whose earlier inputs come from ``state``;
     every query and key head divided by its root mean square (``eps`` inside the root); queries to ``q_out``
-    [T, nh hd], keys and values to the tokens' slots of ``pages`` (see :func:`kv_page_views`)."""
+    [T, nh hd], keys and values to the tokens' slots of ``pages`` (see :func:`kv_page_views`).  ``state`` as in
+    :func:`causal_conv`."""
     S, ss, ld = _rows_in(qkv, "qkv")
     T, C = qkv.shape[-2:]
     assert C == nh * hd + (nkv * (hd + hd_v) if has_kv else 0), (C, nh, nkv, hd, hd_v)

@@ -112,7 +112,8 @@ class GatedPostNormBlock(Block):
             hc = workspace.empty((T, H), dt, dev)
             ops.causal_conv(resid, self.conv_w, state, ctx.q_start, ctx.q_len, ctx.slots, ctx.E, out_conv=hc,
                             out_copy=None if h is resid else h, add_input=True)
-            if self.taps > 1:
+            if self.taps > 1 and any(n > 1 for n in ctx.host_q_len):
+                # (entries of one token were brought up to date by the convolution itself)
                 ops.conv_state_update(resid, state, ctx.q_start, ctx.q_len, ctx.slots, ctx.E)
         else:
             if h is not resid:

@@ -107,7 +107,8 @@ class ConvWindowAttention(Mixer):
         q = workspace.empty((T, nh * hd), x.dtype, x.device)
         ops.qkv_conv_norm_store(qkv, self.bias, self.conv_w, st, ctx.q_start, ctx.q_len, ctx.slots, group.slot_map, ctx.E,
                                 q, kv.pages, nh, nkv, hd, vd, self.eps, ctx.status, use_norm=self.unit_norm)
-        if self.taps > 1:
+        if self.taps > 1 and any(n > 1 for n in ctx.host_q_len):
+            # (entries of one token were brought up to date by the kernel above)
             ops.conv_state_update(qkv, st, ctx.q_start, ctx.q_len, ctx.slots, ctx.E, bias=self.bias)
         out = workspace.empty((T, nh * vd), x.dtype, x.device)
         # no query reads more keys than the window and the kept first ones: no more key slices than those fill
