@@ -2,5 +2,6 @@ from .base import ConfigError, ModelConfig, load_config_dict
 from .engine_config import EngineConfig
 from .qwen3 import Qwen3Config
 from .rimopel import RimopelConfig
+from .nagavik import NagavikConfig
 
-__all__ = ["ConfigError", "ModelConfig", "EngineConfig", "Qwen3Config", "RimopelConfig", "load_config_dict"]
+__all__ = ["ConfigError", "ModelConfig", "EngineConfig", "Qwen3Config", "RimopelConfig", "NagavikConfig", "load_config_dict"]

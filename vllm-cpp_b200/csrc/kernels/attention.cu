@@ -13,7 +13,12 @@
 // window, the first keep_first keys of a request stay visible to every later query
 // (at their true positions); a per-head penalty a_h * ln(1 + b_h * (pos - j)) is
 // taken off the score of key j; values may have another head size than keys (a page
-// is then [nkv][page_size][hd] keys followed by [nkv][page_size][hd_v] values).
+// is then [nkv][page_size][hd] keys followed by [nkv][page_size][hd_v] values); the
+// scaled score may be capped, s <- c tanh(s / c), before a per-head slope times the
+// distance, slope_h (pos - j), is taken off it; and the softmax may have a sink, a
+// silent key of score 0 without a value: w_j = exp(s_j) / (1 + sum_j exp(s_j)).  The
+// sink enters as the starting state (maximum 0, sum 1) of the item's first key slice,
+// so sliced items merge as they are.
 // Items whose key range is sliced write (max, sum, unnormalised output) partials,
 // merged by attn_merge_kernel in slice order.
 #include "common.cuh"
@@ -50,6 +55,11 @@ struct AttnArgs {
     const float* dist_a;
     const float* dist_b;
     int hd_v;
+    // further options: scores capped as c tanh(s / c) (0: no cap); slope_h * (pos - j) taken off the score of key j
+    // (null: none); a silent extra key of score 0 and no value in every softmax (its weight is lost)
+    float softcap;
+    const float* slope;
+    int sink;
 };
 
 template <typename T> struct Vec8;
@@ -144,10 +154,11 @@ __global__ __launch_bounds__(TK) void attn_paged_kernel(AttnArgs a) {
         q_s[r * hd + d] = to_f32(qg[((size_t)(row0 + iq) * a.nh + head0 + ih) * hd + d]) * a.scale;
     }
     if (tid < RMAX) {
-        m_s[tid] = -CUDART_INF_F;
-        l_s[tid] = 0.f;
+        const bool with_sink = a.sink && slice == 0;
+        m_s[tid] = with_sink ? 0.f : -CUDART_INF_F;
+        l_s[tid] = with_sink ? 1.f : 0.f;
         const int h = head0 + tid % gq;
-        da_s[tid] = a.dist_a != nullptr && tid < R ? a.dist_a[h] : 0.f;
+        da_s[tid] = a.dist_a != nullptr && tid < R ? a.dist_a[h] : (a.slope != nullptr && tid < R ? a.slope[h] : 0.f);
         db_s[tid] = a.dist_a != nullptr && tid < R ? a.dist_b[h] : 0.f;
     }
     constexpr int DPT = VCB_MAX_HEAD_DIM / TK;  // output dims per thread
@@ -214,7 +225,9 @@ __global__ __launch_bounds__(TK) void attn_paged_kernel(AttnArgs a) {
                     const int pos = pos0 + r / gq;
                     const bool seen = valid && kidx <= pos && (W <= 0 || kidx > pos - W || kidx < KF);
                     float sc = s[r];
+                    if (a.softcap > 0.f) sc = a.softcap * tanhf(sc / a.softcap);
                     if (a.dist_a != nullptr && seen) sc -= da_s[r] * logf(1.f + db_s[r] * (float)(pos - kidx));
+                    else if (a.slope != nullptr && seen) sc -= da_s[r] * (float)(pos - kidx);
                     p_s[r * TK + tid] = seen ? sc : -CUDART_INF_F;
                 }
             }
@@ -359,8 +372,8 @@ VCB_API int vcb_attn_paged_ex(const void* q, void* out, int dtype, const void* p
                               const int* block_table, const int* table_row, int max_blocks, const int* q_start, const int* q_len,
                               const int* ctx_len, const int* items, int n_items, int rows_max, float* part_o,
                               float* part_ml, int nh, int nkv, int hd, int page_size, int num_pages, int window,
-                              float scale, int keep_first, const float* dist_a, const float* dist_b, int hd_v, int* status,
-                              cudaStream_t stream) {
+                              float scale, int keep_first, const float* dist_a, const float* dist_b, int hd_v,
+                              float softcap, const float* slope, int sink, int* status, cudaStream_t stream) {
     if (n_items == 0) return 0;
     if (hd_v <= 0) hd_v = hd;
     VCB_CHECK_ARG(nh > 0 && nkv > 0 && nh % nkv == 0, "attn_paged: %d query heads are not a multiple of %d KV heads", nh, nkv);
@@ -371,8 +384,11 @@ VCB_API int vcb_attn_paged_ex(const void* q, void* out, int dtype, const void* p
     VCB_CHECK_ARG(rows_max == 8 || rows_max == 32, "attn_paged: rows_max must be 8 or 32");
     VCB_CHECK_ARG(page_size > 0 && window >= 0 && keep_first >= 0, "attn_paged: bad page_size %d, window %d or keep_first %d", page_size, window, keep_first);
     VCB_CHECK_ARG((dist_a == nullptr) == (dist_b == nullptr), "attn_paged: the distance penalty needs both of its vectors");
+    VCB_CHECK_ARG(dist_a == nullptr || slope == nullptr, "attn_paged: a logarithmic penalty and a slope at once");
+    VCB_CHECK_ARG(softcap >= 0.f, "attn_paged: a negative cap");
     AttnArgs a{q, out, pages, page_stride, block_table, table_row, max_blocks, q_start, q_len, ctx_len, items, part_o, part_ml,
-               nh, nkv, hd, page_size, num_pages, window, scale, status, 0, 0, keep_first, dist_a, dist_b, hd_v};
+               nh, nkv, hd, page_size, num_pages, window, scale, status, 0, 0, keep_first, dist_a, dist_b, hd_v,
+               softcap, slope, sink};
     if (dtype == VCB_F32) return rows_max == 8 ? launch_attn<float, 8>(a, n_items, stream) : launch_attn<float, 32>(a, n_items, stream);
     return rows_max == 8 ? launch_attn<__nv_bfloat16, 8>(a, n_items, stream) : launch_attn<__nv_bfloat16, 32>(a, n_items, stream);
 }

@@ -156,7 +156,8 @@ template <typename TOUT>
 __global__ void causal_conv_kernel(RowsIn in, const float* __restrict__ w, float* __restrict__ state,
                                    long long slot_stride, const int* __restrict__ q_start, const int* __restrict__ q_len,
                                    const int* __restrict__ slots, int E, int T, int C, int taps, int add_input,
-                                   TOUT* __restrict__ out_conv, TOUT* __restrict__ out_copy) {
+                                   TOUT* __restrict__ out_conv, TOUT* __restrict__ out_copy, const float* __restrict__ out_bias,
+                                   int act) {
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.y;
@@ -169,6 +170,8 @@ __global__ void causal_conv_kernel(RowsIn in, const float* __restrict__ w, float
     if (out_conv != nullptr) {
         float y = taps > 0 ? conv_at(in, w, state + (long long)slots[e] * slot_stride, C, taps, t, t - q_start[e], c) : 0.f;
         if (add_input) y += u;
+        if (out_bias != nullptr) y += out_bias[c];
+        if (act == 1) y = y / (1.f + expf(-y));
         out_conv[(size_t)t * C + c] = from_f32<TOUT>(y);
     }
     if (taps > 1 && q_len[e] == 1) state_push(state + (long long)slots[e] * slot_stride, C, taps, c, u);
@@ -179,7 +182,8 @@ template <typename TOUT>
 __global__ void causal_conv_vec_kernel(RowsIn in, const float* __restrict__ w, float* __restrict__ state,
                                        long long slot_stride, const int* __restrict__ q_start, const int* __restrict__ q_len,
                                        const int* __restrict__ slots, int E, int T, int C, int taps, int add_input,
-                                       TOUT* __restrict__ out_conv, TOUT* __restrict__ out_copy) {
+                                       TOUT* __restrict__ out_conv, TOUT* __restrict__ out_copy,
+                                       const float* __restrict__ out_bias, int act) {
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.y;
@@ -193,6 +197,14 @@ __global__ void causal_conv_vec_kernel(RowsIn in, const float* __restrict__ w, f
         float4 y = make_float4(0.f, 0.f, 0.f, 0.f);
         if (taps > 0) y = conv_at4(in, w, state + (long long)slots[e] * slot_stride, C, taps, t, t - q_start[e], c);
         if (add_input) { y.x += u.x; y.y += u.y; y.z += u.z; y.w += u.w; }
+        if (out_bias != nullptr) {
+            const float4 b = *reinterpret_cast<const float4*>(out_bias + c);
+            y.x += b.x; y.y += b.y; y.z += b.z; y.w += b.w;
+        }
+        if (act == 1) {
+            y.x = y.x / (1.f + expf(-y.x)); y.y = y.y / (1.f + expf(-y.y));
+            y.z = y.z / (1.f + expf(-y.z)); y.w = y.w / (1.f + expf(-y.w));
+        }
         store4<TOUT>(out_conv + (size_t)t * C + c, y);
     }
     if (taps > 1 && q_len[e] == 1) state_push4(state + (long long)slots[e] * slot_stride, C, taps, c, u);
@@ -455,7 +467,8 @@ __global__ void bias_act_vec_kernel(RowsIn in, TOUT* __restrict__ out, int T, in
             const float x = f[k];
             if (kind == 0) f[k] = 0.5f * x * (1.f + erff(x * 0.70710678118654752440f));
             else if (kind == 1) f[k] = 0.5f * x * (1.f + tanhf(0.79788456080286535588f * (x + 0.044715f * x * x * x)));
-            else f[k] = x / (1.f + expf(-x));
+            else if (kind == 2) f[k] = x / (1.f + expf(-x));
+            else { const float r = fmaxf(x, 0.f); f[k] = r * r; }
         }
         store4<TOUT>(out + (size_t)t * (4 * (size_t)C4) + c, z);
     }
@@ -472,7 +485,8 @@ __global__ void bias_act_kernel(RowsIn in, TOUT* __restrict__ out, long long tot
         float r;
         if (kind == 0) r = 0.5f * z * (1.f + erff(z * 0.70710678118654752440f));
         else if (kind == 1) r = 0.5f * z * (1.f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
-        else r = z / (1.f + expf(-z));
+        else if (kind == 2) r = z / (1.f + expf(-z));
+        else { const float p = fmaxf(z, 0.f); r = p * p; }
         out[i] = from_f32<TOUT>(r);
     }
 }
@@ -490,35 +504,38 @@ VCB_API int vcb_embed_sinusoid(const void* table, int table_dtype, const int* id
 // in: [S][T][ld] 32-bit (+ bias); out_conv = conv(in) (+ in with add_input), out_copy = in, both [T][C] of out_dtype,
 // either may be null.  taps 0: no convolution (out_conv = in with add_input, else zeros).  state [slots][taps-1][C]:
 // read, and for entries of one token brought up to date as well (entries of more need vcb_conv_state_update afterwards).
+// out_bias [C] (or null) is added to the convolution's result, then act (0: none, 1: SiLU) is applied to it.
 VCB_API int vcb_causal_conv(const float* in, int S, long long s_stride, long long ld, const float* bias, const float* w,
                             float* state, long long slot_stride, const int* q_start, const int* q_len,
                             const int* slots, int E, int T, int C, int taps, int add_input, void* out_conv,
-                            void* out_copy, int out_dtype, cudaStream_t stream) {
+                            void* out_copy, int out_dtype, const float* out_bias, int act, cudaStream_t stream) {
     if (T == 0 || C == 0) return 0;
     VCB_CHECK_ARG(taps >= 0 && taps <= MAX_TAPS, "causal_conv: %d taps (0 to %d)", taps, MAX_TAPS);
     VCB_CHECK_ARG(taps < 2 || state != nullptr, "causal_conv: a convolution over %d tokens needs the requests' state", taps);
     VCB_CHECK_ARG(T <= 65535, "causal_conv: %d rows in one step (at most 65535)", T);
     RowsIn r{in, S < 1 ? 1 : S, s_stride, ld, bias};
+    VCB_CHECK_ARG(act == 0 || act == 1, "causal_conv: unknown activation %d", act);
     const bool vec = C % 4 == 0 && rows_vec_ok(r) && (uintptr_t)out_conv % 16 == 0 && (uintptr_t)out_copy % 16 == 0 &&
+                     (uintptr_t)out_bias % 16 == 0 &&
                      (state == nullptr || ((uintptr_t)state % 16 == 0 && slot_stride % 4 == 0));
     if (vec) {
         const dim3 grid4((C / 4 + 127) / 128, T), block4(128);
         if (out_dtype == VCB_F32)
             launch_pdl(causal_conv_vec_kernel<float>, grid4, block4, 0, stream, r, w, state, slot_stride, q_start, q_len, slots, E, T,
-                       C, taps, add_input, (float*)out_conv, (float*)out_copy);
+                       C, taps, add_input, (float*)out_conv, (float*)out_copy, out_bias, act);
         else
             launch_pdl(causal_conv_vec_kernel<__nv_bfloat16>, grid4, block4, 0, stream, r, w, state, slot_stride, q_start, q_len,
-                       slots, E, T, C, taps, add_input, (__nv_bfloat16*)out_conv, (__nv_bfloat16*)out_copy);
+                       slots, E, T, C, taps, add_input, (__nv_bfloat16*)out_conv, (__nv_bfloat16*)out_copy, out_bias, act);
         VCB_CHECK_LAUNCH("causal_conv");
         return 0;
     }
     const dim3 grid((C + 255) / 256, T), block(256);
     if (out_dtype == VCB_F32)
         launch_pdl(causal_conv_kernel<float>, grid, block, 0, stream, r, w, state, slot_stride, q_start, q_len, slots, E, T, C,
-                   taps, add_input, (float*)out_conv, (float*)out_copy);
+                   taps, add_input, (float*)out_conv, (float*)out_copy, out_bias, act);
     else
         launch_pdl(causal_conv_kernel<__nv_bfloat16>, grid, block, 0, stream, r, w, state, slot_stride, q_start, q_len, slots, E,
-                   T, C, taps, add_input, (__nv_bfloat16*)out_conv, (__nv_bfloat16*)out_copy);
+                   T, C, taps, add_input, (__nv_bfloat16*)out_conv, (__nv_bfloat16*)out_copy, out_bias, act);
     VCB_CHECK_LAUNCH("causal_conv");
     return 0;
 }
@@ -612,11 +629,11 @@ VCB_API int vcb_gated_norm_add(float* resid, const float* y, int Sy, long long y
     return 0;
 }
 
-// kind 0: GELU with erf, 1: GELU with tanh, 2: SiLU
+// kind 0: GELU with erf, 1: GELU with tanh, 2: SiLU, 3: the square of ReLU
 VCB_API int vcb_bias_act(const float* in, int S, long long s_stride, long long ld, const float* bias, void* out, int out_dtype,
                          int T, int C, int kind, cudaStream_t stream) {
     if (T == 0 || C == 0) return 0;
-    VCB_CHECK_ARG(kind >= 0 && kind <= 2, "bias_act: unknown activation %d", kind);
+    VCB_CHECK_ARG(kind >= 0 && kind <= 3, "bias_act: unknown activation %d", kind);
     RowsIn r{in, S < 1 ? 1 : S, s_stride, ld, bias};
     const long long total = (long long)T * C;
     if (C % 4 == 0 && rows_vec_ok(r) && (uintptr_t)out % 16 == 0) {

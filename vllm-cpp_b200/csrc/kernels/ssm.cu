@@ -1,0 +1,303 @@
+// A selective state-space recurrence with a scalar decay per head (the Mamba-2 form), over the step's entries:
+//
+//     S_t = exp(-a_h dt_t) S_(t-1) + dt_t B_t x_t^T        S is [N state lanes][P value lanes] per (request, head)
+//     y_t = S_t^T C_t + D_h x_t                            dt_t = softplus(dt_raw_t + dt_bias_h), never clamped
+//
+// Head h reads B and C of group h / (heads / groups).  The state is 32-bit, lives in a slot per request, starts at
+// zero (the step's reset kernel) and is carried from step to step.  Everything that enters the recurrence here is
+// 32-bit: dt from the projection's 32-bit sums, softplus, the decay and its exponential, the products into the state
+// and out of it.  x, B and C come from the short convolution's output in the compute dtype.
+//
+// One token after the other is the only order the recurrence allows, so a long portion is cut into chunks of Q
+// tokens that run side by side:
+//   ssm_chunk_state   every chunk but an entry's last: the state it would end with had it started from zero, and
+//                     the product of its decays;
+//   ssm_chunk_carry   per (entry, head), chunk after chunk: start of chunk c + 1 = decay_c * start of chunk c + local_c,
+//                     the first start being the request's state;
+//   ssm_scan          every chunk from its true start: the outputs y, and the entry's last chunk leaves the
+//                     request's new state.
+// Entries of up to Q tokens (every decoded token) need the last kernel only.  A block is one (chunk, head, tile of
+// value lanes); a thread holds up to 16 state lanes of one value lane in registers, L neighbouring lanes of a warp
+// share a value lane and add their parts of y by shuffles.  B, C, x, dt of 16 tokens at a time are staged in shared
+// memory.  The order of every sum depends on N and L only, not on how a prompt was cut.
+//
+//  * gated_group_norm   out = w * n_g(y * silu(z)): the recurrence's output gated by the z columns of the input
+//                       projection, then cut into equal parts each divided by its own root mean square
+#include "common.cuh"
+
+namespace {
+
+constexpr int NPT = 16;   // state lanes a thread holds at most
+constexpr int NB = 16;    // tokens staged at a time
+
+struct Rows {
+    const float* p;       // [S][T][ld] 32-bit sums
+    int S;
+    long long s_stride;
+    long long ld;
+};
+
+__device__ __forceinline__ float rows_at(const Rows& in, long long t, int c) {
+    float v = 0.f;
+    const float* p = in.p + t * in.ld + c;
+    for (int s = 0; s < in.S; ++s) v += p[(long long)s * in.s_stride];
+    return v;
+}
+
+__device__ __forceinline__ int entry_of_row(const int* __restrict__ q_start, const int* __restrict__ q_len, int E, int t) {
+    int lo = 0, hi = E;
+    while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (q_start[mid] <= t) lo = mid + 1;
+        else hi = mid;
+    }
+    const int e = lo - 1;
+    if (e < 0) return -1;
+    return t - q_start[e] < q_len[e] ? e : -1;
+}
+
+struct SsmArgs {
+    Rows u;               // the input projection's sums; column dt_col + h is head h's raw dt
+    int dt_col;
+    const void* xbc;      // [T][ldx] convolved and activated: x [heads P], then B [groups N], then C [groups N]
+    long long ldx;
+    const float* dt_bias; // [heads]
+    const float* a;       // [heads] decay rates, exp(A_log)
+    const float* D;       // [heads]
+    float* state;         // [slots][heads][P][N]
+    long long slot_stride;
+    const int* q_start;
+    const int* q_len;
+    const int* slots;
+    int E, heads, P, N, groups;
+    int Q;                // tokens per chunk, a multiple of NB
+    float* scratch;       // [chunks][heads][P][N]
+    float* chunk_decay;   // [chunks][heads]
+    float* y;             // [T][heads P]
+    int L, npt, PT;       // lanes per value lane (a power of two up to 32), state lanes per thread, value lanes per block
+};
+
+// which entry and which of its chunks a chunk index is; false when there is no such chunk
+__device__ __forceinline__ bool find_chunk(const SsmArgs& a, int blk, int& e, int& c, int& n, int& base) {
+    int acc = 0;
+    for (int i = 0; i < a.E; ++i) {
+        const int k = (a.q_len[i] + a.Q - 1) / a.Q;
+        if (blk < acc + k) {
+            e = i; c = blk - acc; n = k; base = acc;
+            return true;
+        }
+        acc += k;
+    }
+    return false;
+}
+
+__device__ __forceinline__ float softplus_f(float z) { return fmaxf(z, 0.f) + log1pf(expf(-fabsf(z))); }
+
+// MODE 0: the local end state of a chunk from zero (no output); MODE 1: the outputs from the chunk's true start
+template <typename TX, int MODE>
+__global__ void ssm_scan_kernel(SsmArgs a) {
+    extern __shared__ float sm[];
+    pdl_trigger();
+    pdl_wait();
+    int e, c, n, base;
+    if (!find_chunk(a, blockIdx.x, e, c, n, base)) return;
+    if (MODE == 0 && (n <= 1 || c == n - 1)) return;
+    const int h = blockIdx.y, g = h / (a.heads / a.groups);
+    const int N = a.N, P = a.P, PT = a.PT, L = a.L;
+    float* Bs = sm;                 // [NB][N]
+    float* Cs = Bs + NB * N;        // [NB][N]
+    float* xs = Cs + NB * N;        // [NB][PT]
+    float* dts = xs + NB * PT;      // [NB]
+    float* dAs = dts + NB;          // [NB]
+    const int tid = threadIdx.x;
+    const int pl = tid / L, l = tid % L;
+    const int p = blockIdx.z * PT + pl;
+    const bool active = pl < PT && p < P;
+    const int n0 = l * a.npt;
+    const int cnt = active ? max(0, min(a.npt, N - n0)) : 0;
+    const int inner = a.heads * P;
+    const long long row0 = a.q_start[e] + (long long)c * a.Q;
+    const int len = min(a.Q, a.q_len[e] - c * a.Q);
+    const long long slot = a.slots[e];
+    const size_t hpn = ((size_t)h * P + (active ? p : 0)) * N + n0;
+
+    float S[NPT];
+#pragma unroll
+    for (int i = 0; i < NPT; ++i) S[i] = 0.f;
+    if (MODE == 1) {
+        const float* src = n > 1 ? a.scratch + (size_t)(base + c) * a.heads * P * N : a.state + slot * a.slot_stride;
+#pragma unroll
+        for (int i = 0; i < NPT; ++i)
+            if (i < cnt) S[i] = src[hpn + i];
+    }
+    const float rate = a.a[h], bias = a.dt_bias[h], Dh = a.D[h];
+    const TX* xbc = reinterpret_cast<const TX*>(a.xbc);
+    float decay = 1.f;
+    for (int j0 = 0; j0 < len; j0 += NB) {
+        const int nb = min(NB, len - j0);
+        __syncthreads();
+        for (int i = tid; i < nb * N; i += blockDim.x) {
+            const int j = i / N, k = i % N;
+            const TX* row = xbc + (row0 + j0 + j) * a.ldx;
+            Bs[j * N + k] = to_f32(row[inner + g * N + k]);
+            Cs[j * N + k] = to_f32(row[inner + (a.groups + g) * N + k]);
+        }
+        for (int i = tid; i < nb * PT; i += blockDim.x) {
+            const int j = i / PT, k = i % PT;
+            const int pp = blockIdx.z * PT + k;
+            xs[j * PT + k] = pp < P ? to_f32(xbc[(row0 + j0 + j) * a.ldx + h * P + pp]) : 0.f;
+        }
+        if (tid < nb) {
+            const float dt = softplus_f(rows_at(a.u, row0 + j0 + tid, a.dt_col + h) + bias);
+            dts[tid] = dt;
+            dAs[tid] = expf(-rate * dt);
+        }
+        __syncthreads();
+        for (int j = 0; j < nb; ++j) {
+            const float dA = dAs[j];
+            const float xv = active ? xs[j * PT + pl] : 0.f;
+            const float dtx = dts[j] * xv;
+            const float* Bj = Bs + j * N + n0;
+            const float* Cj = Cs + j * N + n0;
+            float acc = 0.f;
+#pragma unroll
+            for (int i = 0; i < NPT; ++i) {
+                if (i < cnt) {
+                    S[i] = fmaf(S[i], dA, dtx * Bj[i]);
+                    if (MODE == 1) acc = fmaf(S[i], Cj[i], acc);
+                }
+            }
+            if (MODE == 1) {
+                for (int o = L >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+                if (l == 0 && active) a.y[(size_t)(row0 + j0 + j) * inner + h * P + p] = fmaf(Dh, xv, acc);
+            } else {
+                decay *= dA;
+            }
+        }
+    }
+    if (MODE == 0) {
+        float* dst = a.scratch + (size_t)(base + c) * a.heads * P * N;
+#pragma unroll
+        for (int i = 0; i < NPT; ++i)
+            if (i < cnt) dst[hpn + i] = S[i];
+        if (tid == 0 && blockIdx.z == 0) a.chunk_decay[(size_t)(base + c) * a.heads + h] = decay;
+    } else if (c == n - 1) {
+        float* dst = a.state + slot * a.slot_stride;
+#pragma unroll
+        for (int i = 0; i < NPT; ++i)
+            if (i < cnt) dst[hpn + i] = S[i];
+    }
+}
+
+// grid (entries, heads); the threads walk the head's P x N state elements
+__global__ void ssm_chunk_carry_kernel(SsmArgs a) {
+    pdl_trigger();
+    pdl_wait();
+    const int e = blockIdx.x, h = blockIdx.y;
+    const int n = (a.q_len[e] + a.Q - 1) / a.Q;
+    if (n <= 1) return;
+    int base = 0;
+    for (int i = 0; i < e; ++i) base += (a.q_len[i] + a.Q - 1) / a.Q;
+    const size_t per_head = (size_t)a.P * a.N, per_chunk = per_head * a.heads;
+    const float* st = a.state + (long long)a.slots[e] * a.slot_stride + h * per_head;
+    for (size_t i = threadIdx.x; i < per_head; i += blockDim.x) {
+        float S = st[i];
+        for (int c = 0; c < n; ++c) {
+            float* at = a.scratch + (size_t)(base + c) * per_chunk + h * per_head + i;
+            const float local = c < n - 1 ? *at : 0.f;
+            *at = S;
+            if (c < n - 1) S = fmaf(a.chunk_decay[(size_t)(base + c) * a.heads + h], S, local);
+        }
+    }
+}
+
+// grid (rows, parts): out[t, c] = w[c] * v / sqrt(mean over the part of v^2 + eps), v = y[t, c] * silu(z[t, c])
+template <typename TOUT>
+__global__ void gated_group_norm_kernel(const float* __restrict__ y, Rows z, const float* __restrict__ w, float eps,
+                                        const int* __restrict__ q_start, const int* __restrict__ q_len, int E, int C, int gs,
+                                        TOUT* __restrict__ out) {
+    extern __shared__ float vals[];   // [gs] then 33 floats
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x, c0 = blockIdx.y * gs;
+    if (entry_of_row(q_start, q_len, E, t) < 0) return;
+    float ss = 0.f;
+    for (int k = threadIdx.x; k < gs; k += blockDim.x) {
+        const float zz = rows_at(z, t, c0 + k);
+        const float v = y[(size_t)t * C + c0 + k] * (zz / (1.f + expf(-zz)));
+        vals[k] = v;
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, vals + gs);
+    const float mul = 1.f / sqrtf(ss / (float)gs + eps);
+    for (int k = threadIdx.x; k < gs; k += blockDim.x)
+        out[(size_t)t * C + c0 + k] = from_f32<TOUT>(vals[k] * mul * w[c0 + k]);
+}
+
+}  // namespace
+
+// The three kernels of the recurrence.  u: the input projection's sums [S][T][ld] (dt of head h in column dt_col + h);
+// xbc [T][ldx] of xbc_dtype; state [slots][heads][P][N]; y [T][heads P] 32-bit.  n_chunks: how many chunks of Q tokens the
+// step's entries can have (the sum over entries of ceil(q_len / Q), or more); multi: whether any entry may have more
+// than one chunk (then scratch [n_chunks][heads][P][N] and chunk_decay [n_chunks][heads] are needed).
+VCB_API int vcb_ssm_scan(const float* u, int S, long long s_stride, long long ld, int dt_col, const void* xbc, int xbc_dtype,
+                         long long ldx, const float* dt_bias, const float* a_rate, const float* D, float* state,
+                         long long slot_stride, const int* q_start, const int* q_len, const int* slots, int E, int heads, int P,
+                         int N, int groups, int Q, int n_chunks, int multi, float* scratch, float* chunk_decay, float* y,
+                         cudaStream_t stream) {
+    if (n_chunks == 0 || E == 0) return 0;
+    VCB_CHECK_ARG(heads > 0 && groups > 0 && heads % groups == 0, "ssm_scan: %d heads are not a multiple of %d groups", heads, groups);
+    VCB_CHECK_ARG(N >= 1 && N <= NPT * 32, "ssm_scan: %d state lanes (1 to %d)", N, NPT * 32);
+    VCB_CHECK_ARG(P >= 1 && Q >= NB && Q % NB == 0, "ssm_scan: bad sizes P=%d Q=%d", P, Q);
+    VCB_CHECK_ARG(!multi || (scratch != nullptr && chunk_decay != nullptr), "ssm_scan: chunks need their scratch");
+    VCB_CHECK_ARG(n_chunks <= 0x7fffffff / 1 && heads <= 65535 && E <= 65535, "ssm_scan: too many heads or entries");
+    int L = 1;
+    while (L * NPT < N) L <<= 1;
+    const int npt = (N + L - 1) / L;
+    int PT = 256 / L;
+    if (PT < 1) PT = 1;
+    if (PT > P) PT = P;
+    const int threads = (PT * L + 31) / 32 * 32;
+    const int ptiles = (P + PT - 1) / PT;
+    VCB_CHECK_ARG(ptiles <= 65535, "ssm_scan: too many tiles of value lanes");
+    SsmArgs args{Rows{u, S < 1 ? 1 : S, s_stride, ld}, dt_col, xbc, ldx, dt_bias, a_rate, D, state, slot_stride, q_start, q_len,
+                 slots, E, heads, P, N, groups, Q, scratch, chunk_decay, y, L, npt, PT};
+    const size_t smem = ((size_t)2 * NB * N + (size_t)NB * PT + 2 * NB) * sizeof(float);
+    const dim3 grid(n_chunks, heads, ptiles);
+    const bool f32 = xbc_dtype == VCB_F32;
+    if (multi) {
+        if (f32) launch_pdl(ssm_scan_kernel<float, 0>, grid, dim3(threads), smem, stream, args);
+        else launch_pdl(ssm_scan_kernel<__nv_bfloat16, 0>, grid, dim3(threads), smem, stream, args);
+        VCB_CHECK_LAUNCH("ssm_chunk_state");
+        launch_pdl(ssm_chunk_carry_kernel, dim3(E, heads), dim3(256), 0, stream, args);
+        VCB_CHECK_LAUNCH("ssm_chunk_carry");
+    }
+    if (f32) launch_pdl(ssm_scan_kernel<float, 1>, grid, dim3(threads), smem, stream, args);
+    else launch_pdl(ssm_scan_kernel<__nv_bfloat16, 1>, grid, dim3(threads), smem, stream, args);
+    VCB_CHECK_LAUNCH("ssm_scan");
+    return 0;
+}
+
+// y [T][C] 32-bit; z: 32-bit sums [S][T][ld] whose first C columns gate y; w [C]; parts equal pieces of the row
+VCB_API int vcb_gated_group_norm(const float* y, const float* z, int S, long long s_stride, long long ld, const float* w,
+                                 float eps, const int* q_start, const int* q_len, int E, int T, int C, int parts, void* out,
+                                 int out_dtype, cudaStream_t stream) {
+    if (T == 0 || C == 0) return 0;
+    VCB_CHECK_ARG(parts >= 1 && C % parts == 0 && parts <= 65535, "gated_group_norm: %d channels in %d parts", C, parts);
+    const int gs = C / parts;
+    Rows rz{z, S < 1 ? 1 : S, s_stride, ld};
+    const size_t smem = ((size_t)gs + 64) * sizeof(float);
+    VCB_CHECK_ARG(smem <= 200 * 1024, "gated_group_norm: parts of %d channels are too long", gs);
+    const int threads = gs >= 2048 ? 1024 : (gs >= 512 ? 512 : 256);
+    if (out_dtype == VCB_F32) {
+        auto kern = gated_group_norm_kernel<float>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        launch_pdl(kern, dim3(T, parts), dim3(threads), smem, stream, y, rz, w, eps, q_start, q_len, E, C, gs, (float*)out);
+    } else {
+        auto kern = gated_group_norm_kernel<__nv_bfloat16>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        launch_pdl(kern, dim3(T, parts), dim3(threads), smem, stream, y, rz, w, eps, q_start, q_len, E, C, gs, (__nv_bfloat16*)out);
+    }
+    VCB_CHECK_LAUNCH("gated_group_norm");
+    return 0;
+}

@@ -8,6 +8,7 @@ from ..parts import BuildContext  # registers the parts
 from ..registry import architecture_of, get_architecture
 from . import qwen3  # registers Qwen3ForCausalLM
 from . import rimopel  # registers Rimopel
+from . import nagavik  # registers Nagavik
 from .decoder import DecoderModel
 
 

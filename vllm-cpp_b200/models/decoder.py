@@ -124,6 +124,9 @@ class DecoderModel:
         workspace.end_runs()
         if ctx.n_rows == 0:
             return None
+        if self.final_norm is None and hasattr(pending, "add"):
+            pending.add(resid)      # (a result that its arrangement left to be normed, scaled and added)
+            pending = None
         if self.final_norm is None:
             # an architecture without a final norm: the head reads the wanted rows of the stream as they are
             x = resid if pending is None else resid + (pending.sum(0) if pending.dim() == 3 else pending).float()

@@ -69,9 +69,20 @@ def _declare(L):
         "vcb_sgemm_tn": [P, P, P, I, I, I, LL, LL, LL, P],
         "vcb_gemm_bf16_plain": [P, P, P, I, I, I, I, LL, LL, LL, P],
         "vcb_attn_paged": [P, P, I, P, LL, P, P, I, P, P, P, P, I, I, P, P, I, I, I, I, I, I, F, P, P],
-        "vcb_attn_paged_ex": [P, P, I, P, LL, P, P, I, P, P, P, P, I, I, P, P, I, I, I, I, I, I, F, I, P, P, I, P, P],
+        "vcb_attn_paged_ex": [P, P, I, P, LL, P, P, I, P, P, P, P, I, I, P, P, I, I, I, I, I, I, F, I, P, P, I, F, P, I, P, P],
         "vcb_embed_sinusoid": [P, I, P, P, P, P, I, I, I, P, P],
-        "vcb_causal_conv": [P, I, LL, LL, P, P, P, LL, P, P, P, I, I, I, I, I, P, P, I, P],
+        "vcb_causal_conv": [P, I, LL, LL, P, P, P, LL, P, P, P, I, I, I, I, I, P, P, I, P, I, P],
+        "vcb_embed_scaled_pos": [P, I, P, P, P, I, F, P, I, I, I, I, P, P],
+        "vcb_postnorm_add_norm": [P, P, I, LL, LL, P, P, P, F, P, P, I, I, I, P, F, P, I, P, I, P],
+        "vcb_qkv_wholenorm_store": [P, I, LL, LL, P, P, F, P, P, P, I, I, I, I, I, I, P, P, LL, I, I, I, P, P],
+        "vcb_gated_act": [P, I, LL, LL, P, P, I, I, I, I, P],
+        "vcb_softcap": [P, LL, F, P],
+        "vcb_ssm_scan": [P, I, LL, LL, I, P, I, LL, P, P, P, P, LL, P, P, P, I, I, I, I, I, I, I, I, P, P, P, P],
+        "vcb_gated_group_norm": [P, P, I, LL, LL, P, F, P, P, I, I, I, I, P, I, P],
+        "vcb_moe_route": [P, I, LL, LL, P, P, I, I, I, I, I, P, P, P],
+        "vcb_moe_group": [P, I, I, I, P, P, P, P],
+        "vcb_moe_gemm": [P, LL, P, I, P, P, P, I, I, P, I, I, I, I, P],
+        "vcb_moe_combine": [P, P, P, I, P, I, LL, LL, P, P, I, I, I, P, P],
         "vcb_conv_state_update": [P, I, LL, LL, P, P, LL, P, P, P, I, I, I, P],
         "vcb_qkv_conv_norm_store": [P, I, LL, LL, P, P, P, LL, P, P, P, P, I, I, I, I, I, I, I, I, F, P, P, LL, I, I, I, I, P, P],
         "vcb_gated_norm_add": [P, P, I, LL, LL, P, I, LL, LL, P, P, F, P, P, I, I, I, P, I, P],
@@ -394,10 +405,13 @@ def kv_page_views(pages, nkv, hd, hd_v):
 
 
 def attn_window_bias(q, out, pages, block_table, q_start, q_len, ctx_len, items, n_items, rows_max, part_o, part_ml,
-                     nh, nkv, hd, window, status, table_row=None, *, scale, keep_first=0, dist_a=None, dist_b=None, hd_v=None):
+                     nh, nkv, hd, window, status, table_row=None, *, scale, keep_first=0, dist_a=None, dist_b=None, hd_v=None,
+                     softcap=0.0, slope=None, sink=False):
     """:func:`attn_paged` with its options: scores scaled by ``scale``; with a window, the first ``keep_first`` keys of
     a request stay visible; ``dist_a``/``dist_b`` (float32 [nh]): a_h ln(1 + b_h (pos - j)) is taken off key j's
-    score; values of head size ``hd_v`` (``pages`` then [num_pages, nkv * page_size * (hd + hd_v)])."""
+    score; values of head size ``hd_v`` (``pages`` then [num_pages, nkv * page_size * (hd + hd_v)]); ``softcap`` c > 0:
+    the scaled score becomes c tanh(s / c); ``slope`` (float32 [nh]): slope_h (pos - j) is taken off after the cap;
+    ``sink``: a silent key of score 0 and no value takes part in every softmax."""
     hd_v = hd if hd_v is None else int(hd_v)
     _need(q, "q"); _need(out, "out", q.dtype); _need(pages, "pages", q.dtype)
     for name, t in (("block_table", block_table), ("q_start", q_start), ("q_len", q_len), ("ctx_len", ctx_len),
@@ -407,10 +421,13 @@ def attn_window_bias(q, out, pages, block_table, q_start, q_len, ctx_len, items,
     if dist_a is not None:
         _need(dist_a, "dist_a", torch.float32); _need(dist_b, "dist_b", torch.float32)
         assert dist_a.numel() == nh and dist_b.numel() == nh
+    if slope is not None:
+        _need(slope, "slope", torch.float32)
+        assert slope.numel() == nh
     _call("vcb_attn_paged_ex", _p(q), _p(out), _dt(q), _p(pages), pages.stride(0), _p(block_table), _p(table_row),
           block_table.shape[1], _p(q_start), _p(q_len), _p(ctx_len), _p(items), n_items, rows_max, _p(part_o), _p(part_ml),
           nh, nkv, hd, page_size, num_pages, int(window or 0), float(scale), int(keep_first or 0), _p(dist_a), _p(dist_b),
-          hd_v, _p(status), _stream())
+          hd_v, float(softcap or 0.0), _p(slope), int(bool(sink)), _p(status), _stream())
 
 
 def embed_sinusoid(table, ids, positions, inv_freq, out, status):
@@ -433,14 +450,19 @@ def _rows_in(t: torch.Tensor, name: str):
 
 
 def causal_conv(x, weight, state, q_start, q_len, slots, n_entries, out_conv=None, out_copy=None, bias=None,
-                add_input=False):
+                add_input=False, out_bias=None, act=None):
     """Per channel, over the tokens of each entry: out_conv[t] = sum_j weight[:, j] x[t - taps + 1 + j] (+ x[t] with
     ``add_input``), the taps - 1 inputs before an entry's first row read from ``state`` [slots, taps - 1, C] (32-bit)
     at the entry's slot; out_copy[t] = x[t].  x: 32-bit [T, C] or [S, T, C] partial sums, ``bias`` [C] added.
     ``weight`` None: no convolution.  Rows outside every entry are left alone.  The state row of an entry that brought
-    one token is brought up to date as well; entries of more tokens need :func:`conv_state_update` afterwards."""
+    one token is brought up to date as well; entries of more tokens need :func:`conv_state_update` afterwards.
+    ``out_bias`` [C] is added to the convolution's result, then ``act`` ("silu" or None) is applied to it."""
     S, ss, ld = _rows_in(x, "x")
     T, C = x.shape[-2:]
+    if out_bias is not None:
+        _need(out_bias, "out_bias", torch.float32); assert out_bias.numel() == C
+    if act not in (None, "silu"):
+        raise KernelError(f"causal_conv: activation '{act}' (None or 'silu')")
     taps = 0 if weight is None else weight.shape[1]
     if weight is not None:
         _need(weight, "weight", torch.float32); assert weight.shape[0] == C
@@ -453,7 +475,7 @@ def causal_conv(x, weight, state, q_start, q_len, slots, n_entries, out_conv=Non
     assert dt is not None
     _call("vcb_causal_conv", _p(x), S, ss, ld, _p(bias), _p(weight), _p(state) if taps > 1 else None,
           state.stride(0) if taps > 1 else 0, _p(q_start), _p(q_len), _p(slots), n_entries, T, C, taps, int(bool(add_input)),
-          _p(out_conv), _p(out_copy), dt, _stream())
+          _p(out_conv), _p(out_copy), dt, _p(out_bias), 1 if act == "silu" else 0, _stream())
 
 
 def conv_state_update(x, state, q_start, q_len, slots, n_entries, bias=None):
@@ -516,7 +538,7 @@ def gated_norm_add(resid, y, gate, gate_bias, weight, eps, q_start, q_len, n_ent
           _stream())
 
 
-ACTIVATIONS = {"gelu": 0, "gelu_erf": 0, "gelu_tanh": 1, "silu": 2}
+ACTIVATIONS = {"gelu": 0, "gelu_erf": 0, "gelu_tanh": 1, "silu": 2, "relu2": 3}
 
 
 def bias_act(x, out, kind: str, bias=None):
@@ -527,6 +549,182 @@ def bias_act(x, out, kind: str, bias=None):
     if kind not in ACTIVATIONS:
         raise KernelError(f"activation '{kind}' is not one of {sorted(ACTIVATIONS)}")
     _call("vcb_bias_act", _p(x), S, ss, ld, _p(bias), _p(out), _dt(out), T, C, ACTIVATIONS[kind], _stream())
+
+
+def embed_scaled_pos(table, ids, positions, pos_table, scale, out, status):
+    """out[t] = scale * table[ids[t]] + pos_table[positions[t]]."""
+    _need(table, "table"); _need(pos_table, "pos_table"); _need(ids, "ids", torch.int32)
+    _need(positions, "positions", torch.int32); _need(out, "out", torch.float32)
+    T, H = out.shape
+    assert table.shape[1] == H and pos_table.shape[1] == H and ids.numel() >= T and positions.numel() >= T
+    _call("vcb_embed_scaled_pos", _p(table), _dt(table), _p(ids), _p(positions), _p(pos_table), _dt(pos_table), float(scale),
+          _p(out), T, H, table.shape[0], pos_table.shape[0], _p(status), _stream())
+
+
+def postnorm_add_norm(resid, y, post_weight, eps, q_start, q_len, n_entries, *, y_bias=None, layer_scale=None,
+                      next_weight=None, next_eps=None, out=None, rows=None):
+    """resid[t] += layer_scale * post_weight * n(y[t] + y_bias), n(v) = v / sqrt(mean(v^2) + eps), for the rows of the
+    step's entries; then out[t] = next_weight * n'(resid[t]) with ``next_eps`` inside its root.  y: 32-bit [T, H] or
+    [S, T, H] partial sums, or None (nothing is added: a plain norm).  ``rows`` (int32): only those rows, the stream is
+    left as it is and ``out`` is [len(rows), H]."""
+    _need(resid, "resid", torch.float32)
+    T, H = resid.shape
+    Sy = ssy = ldy = 0
+    if y is not None:
+        Sy, ssy, ldy = _rows_in(y, "y")
+        assert y.shape[-1] == H and y.shape[-2] >= T
+        _need(post_weight, "post_weight", torch.float32)
+    for name, t in (("y_bias", y_bias), ("layer_scale", layer_scale), ("next_weight", next_weight)):
+        if t is not None:
+            _need(t, name, torch.float32); assert t.numel() == H
+    n = T
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+        n = rows.numel()
+    if out is not None:
+        _need(out, "out"); assert out.shape == (n, H) and next_weight is not None
+    _call("vcb_postnorm_add_norm", _p(resid), _p(y), Sy, ssy, ldy, _p(y_bias) if y is not None else None, _p(post_weight),
+          _p(layer_scale), float(eps), _p(q_start), _p(q_len), n_entries, T, H, _p(next_weight),
+          float(eps if next_eps is None else next_eps), _p(out), _dt(out) if out is not None else F32, _p(rows), n, _stream())
+
+
+def qkv_wholenorm_store(qkv, q_weight, k_weight, eps, q_start, q_len, slot_map, n_entries, q_out, pages, nh, nkv, hd, hd_v,
+                        status):
+    """The stacked q, k, v projection ``qkv`` (32-bit [T, C] or [S, T, C], C = nh hd + nkv (hd + hd_v)): all of a token's
+    query lanes divided by their common root mean square and multiplied by ``q_weight`` [nh hd], its key lanes likewise
+    with ``k_weight`` [nkv hd] (both None: no norm); queries to ``q_out``, keys and values to the tokens' slots of
+    ``pages`` (see :func:`kv_page_views`)."""
+    S, ss, ld = _rows_in(qkv, "qkv")
+    T, C = qkv.shape[-2:]
+    assert C == nh * hd + nkv * (hd + hd_v), (C, nh, nkv, hd, hd_v)
+    if q_weight is not None:
+        _need(q_weight, "q_weight", torch.float32); _need(k_weight, "k_weight", torch.float32)
+        assert q_weight.numel() == nh * hd and k_weight.numel() == nkv * hd
+    _need(q_out, "q_out"); assert q_out.shape == (T, nh * hd)
+    _need(pages, "pages", q_out.dtype); _need(slot_map, "slot_map", torch.int32)
+    page_size, num_pages = kv_page_views(pages, nkv, hd, hd_v)
+    _call("vcb_qkv_wholenorm_store", _p(qkv), S, ss, ld, _p(q_weight), _p(k_weight), float(eps), _p(q_start), _p(q_len),
+          _p(slot_map), n_entries, T, nh, nkv, hd, hd_v, _p(q_out), _p(pages), pages.stride(0), page_size, num_pages,
+          _dt(q_out), _p(status), _stream())
+
+
+def gated_act(x, out, kind: str, bias=None):
+    """out[t, i] = act(x[t, i] + bias[i]) * (x[t, I + i] + bias[I + i]): x 32-bit [T, 2 I] or [S, T, 2 I] partial sums,
+    the gate's columns first; ``kind`` one of ACTIVATIONS."""
+    S, ss, ld = _rows_in(x, "x")
+    T, I2 = x.shape[-2:]
+    _need(out, "out"); assert out.shape == (T, I2 // 2) and I2 % 2 == 0
+    if kind not in ACTIVATIONS:
+        raise KernelError(f"activation '{kind}' is not one of {sorted(ACTIVATIONS)}")
+    if bias is not None:
+        _need(bias, "bias", torch.float32); assert bias.numel() == I2
+    _call("vcb_gated_act", _p(x), S, ss, ld, _p(bias), _p(out), _dt(out), T, I2 // 2, ACTIVATIONS[kind], _stream())
+
+
+def softcap(z, cap):
+    """z <- cap * tanh(z / cap), in place (32-bit)."""
+    _need(z, "z", torch.float32)
+    _call("vcb_softcap", _p(z), z.numel(), float(cap), _stream())
+
+
+SSM_STAGE = 16     # tokens the recurrence stages at a time; a chunk is a multiple of it
+
+
+def ssm_scan(u, dt_col, xbc, dt_bias, rate, skip, state, q_start, q_len, slots, n_entries, heads, P, N, groups, y, *,
+             chunk, n_chunks, scratch=None, chunk_decay=None):
+    """S <- exp(-rate_h dt) S + dt B x^T, y = S^T C + skip_h x per head over the step's entries, the state carried in
+    ``state`` [slots, heads, P, N] (32-bit).  ``u``: 32-bit sums [T, C] or [S, T, C] whose column ``dt_col + h`` is head
+    h's raw dt (softplus(dt + dt_bias_h) is taken here); ``xbc`` [T, heads P + 2 groups N]: x, then B, then C, in the
+    compute dtype; ``y`` [T, heads P] 32-bit.  Entries are cut into chunks of ``chunk`` tokens; ``n_chunks`` bounds their
+    number over the step; with ``scratch`` [n_chunks, heads, P, N] and ``chunk_decay`` [n_chunks, heads] entries of more
+    than one chunk run their chunks side by side (without them every entry must fit one chunk)."""
+    S, ss, ld = _rows_in(u, "u")
+    _need(xbc, "xbc", contiguous=False); _need(state, "state", torch.float32); _need(y, "y", torch.float32)
+    for name, t in (("dt_bias", dt_bias), ("rate", rate), ("skip", skip)):
+        _need(t, name, torch.float32); assert t.numel() == heads
+    T = u.shape[-2]
+    assert xbc.stride(1) == 1 and xbc.shape == (T, heads * P + 2 * groups * N) and y.shape == (T, heads * P)
+    assert state.shape[1:] == (heads, P, N) and chunk % SSM_STAGE == 0
+    multi = scratch is not None
+    if multi:
+        _need(scratch, "scratch", torch.float32); _need(chunk_decay, "chunk_decay", torch.float32)
+        assert scratch.numel() >= n_chunks * heads * P * N and chunk_decay.numel() >= n_chunks * heads
+    global launch_count
+    _call("vcb_ssm_scan", _p(u), S, ss, ld, int(dt_col), _p(xbc), _dt(xbc), xbc.stride(0), _p(dt_bias), _p(rate), _p(skip),
+          _p(state), state.stride(0), _p(q_start), _p(q_len), _p(slots), n_entries, heads, P, N, groups, int(chunk),
+          int(n_chunks), int(multi), _p(scratch), _p(chunk_decay), _p(y), _stream())
+    if multi:
+        launch_count += 2   # three kernels
+
+
+def gated_group_norm(y, z, weight, eps, q_start, q_len, n_entries, parts, out):
+    """out = weight * n_g(y * silu(z)): y 32-bit [T, C]; z 32-bit sums [T, >= C] or [S, T, >= C] whose first C columns
+    gate y; the row is cut into ``parts`` equal pieces, each divided by its own root mean square."""
+    _need(y, "y", torch.float32); _need(weight, "weight", torch.float32); _need(out, "out")
+    T, C = y.shape
+    S, ss, ld = _rows_in(z, "z")
+    assert z.shape[-1] >= C and z.shape[-2] >= T and out.shape == (T, C) and weight.numel() == C
+    _call("vcb_gated_group_norm", _p(y), _p(z), S, ss, ld, _p(weight), float(eps), _p(q_start), _p(q_len), n_entries, T, C,
+          int(parts), _p(out), _dt(out), _stream())
+
+
+@functools.lru_cache(maxsize=None)
+def moe_tile_rows() -> int:
+    """Rows of a tile of the experts' products: every expert's (token, choice) pairs are padded to a multiple of it."""
+    return int(lib().vcb_moe_tile_rows())
+
+
+def moe_tiles_cap(n_pairs: int, n_experts: int) -> int:
+    """The most tiles ``n_pairs`` pairs can fill when each of ``n_experts`` experts pads its own to whole tiles."""
+    return min(n_pairs, n_experts) + n_pairs // moe_tile_rows()
+
+
+def moe_route(logits, q_start, q_len, n_entries, top, sel_e, sel_w, softmax_weights=False):
+    """Per row of the step's entries: the ``top`` largest of the router's ``logits`` (32-bit [T, E] or [S, T, E]) ->
+    ``sel_e`` [T, top] int32 (-1 in rows outside every entry) and ``sel_w`` [T, top]: sigmoid(logit), or the softmax over
+    the chosen logits."""
+    S, ss, ld = _rows_in(logits, "logits")
+    T, E = logits.shape[-2:]
+    _need(sel_e, "sel_e", torch.int32); _need(sel_w, "sel_w", torch.float32)
+    assert sel_e.numel() == T * top and sel_w.numel() == T * top
+    _call("vcb_moe_route", _p(logits), S, ss, ld, _p(q_start), _p(q_len), n_entries, T, E, int(top), int(bool(softmax_weights)),
+          _p(sel_e), _p(sel_w), _stream())
+
+
+def moe_group(sel_e, n_experts, tiles_cap, pos_of, src_of, tile_expert):
+    """Sorts the pairs by expert into tiles (see csrc/kernels/moe.cu)."""
+    for name, t in (("sel_e", sel_e), ("pos_of", pos_of), ("src_of", src_of), ("tile_expert", tile_expert)):
+        _need(t, name, torch.int32)
+    A = sel_e.numel()
+    assert pos_of.numel() == A and src_of.numel() == tiles_cap * moe_tile_rows() and tile_expert.numel() == tiles_cap
+    _call("vcb_moe_group", _p(sel_e), A, int(n_experts), int(tiles_cap), _p(pos_of), _p(src_of), _p(tile_expert), _stream())
+
+
+def moe_gemm(x, w, tile_expert, out, *, src_of=None, sel_w=None, top=1, act=None):
+    """The experts' product over the sorted tiles: w [E, N, K]; with ``src_of`` x is the tokens' rows [T, K], read through
+    the sorted order and multiplied by the pairs' ``sel_w`` (None: as they are); without it x is [tiles * rows, K] in
+    sorted order.  ``act``: out [tiles * rows, N] in the compute dtype after that activation; None: 32-bit sums."""
+    _need(x, "x", w.dtype, contiguous=False); _need(w, "w"); _need(tile_expert, "tile_expert", torch.int32)
+    E, N, K = w.shape
+    tiles = tile_expert.numel()
+    assert x.shape[1] == K and x.stride(1) == 1 and out.shape == (tiles * moe_tile_rows(), N)
+    _need(out, "out", w.dtype if act is not None else torch.float32)
+    if act is not None and act not in ACTIVATIONS:
+        raise KernelError(f"activation '{act}' is not one of {sorted(ACTIVATIONS)}")
+    _call("vcb_moe_gemm", _p(x), x.stride(0), _p(w), _dt(w), _p(tile_expert), _p(src_of), _p(sel_w), int(top),
+          int(src_of is not None), _p(out), N, K, ACTIVATIONS[act] if act is not None else -1, tiles, _stream())
+
+
+def moe_combine(y, pos_of, top, q_start, q_len, n_entries, out, shared=None, sel_w=None):
+    """out[t] = shared[t] + sum over the token's pairs of y[pos_of[t, k]] (times sel_w[t, k] if given), k in order."""
+    _need(y, "y", torch.float32); _need(pos_of, "pos_of", torch.int32); _need(out, "out", torch.float32)
+    T, W = out.shape
+    S = ss = ld = 0
+    if shared is not None:
+        S, ss, ld = _rows_in(shared, "shared")
+        assert shared.shape[-1] == W and shared.shape[-2] >= T
+    _call("vcb_moe_combine", _p(y), _p(pos_of), _p(sel_w), int(top), _p(shared), S, ss, ld, _p(q_start), _p(q_len), n_entries,
+          T, W, _p(out), _stream())
 
 
 def attn_merge(part_o, part_ml, dec_rows, out, n_dec, nh, hd, nslices):

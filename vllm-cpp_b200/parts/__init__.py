@@ -3,9 +3,12 @@ from ..registry import register_part
 from .attention import GQAAttention
 from .base import Block, BuildContext, CacheSpec, FeedForward, Mixer, Norm, Part, PositionEncoding
 from .block import PreNormBlock
-from .embedding import Embedding, Head, LMHead, SinusoidalTokenEmbedding, TokenEmbedding
+from .embedding import Embedding, Head, LMHead, PositionalTokenEmbedding, SinusoidalTokenEmbedding, TokenEmbedding
 from .gated_block import GatedPostNormBlock
-from .mlp import DenseMLP, SwiGLUMLP
+from .mamba2 import Mamba2Mixer
+from .mlp import DenseMLP, GatedMLP, SwiGLUMLP
+from .moe import RoutedExperts
+from .sandwich_block import SandwichNormBlock
 from .window_attention import ConvWindowAttention
 from .norm import RMSNorm
 from .rope import RotaryEmbedding
@@ -21,7 +24,13 @@ register_part("block", "gated_postnorm", GatedPostNormBlock)
 register_part("embedding", "token_embedding", TokenEmbedding)
 register_part("embedding", "sinusoidal_token_embedding", SinusoidalTokenEmbedding)
 register_part("head", "lm_head", LMHead)
+register_part("embedding", "positional_token_embedding", PositionalTokenEmbedding)
+register_part("mixer", "mamba2", Mamba2Mixer)
+register_part("feed_forward", "gated_mlp", GatedMLP)
+register_part("feed_forward", "routed_experts", RoutedExperts)
+register_part("block", "sandwich_norm", SandwichNormBlock)
 
 __all__ = ["Block", "BuildContext", "CacheSpec", "FeedForward", "Mixer", "Norm", "Part", "PositionEncoding",
            "PreNormBlock", "Embedding", "Head", "LMHead", "TokenEmbedding", "SwiGLUMLP", "DenseMLP", "GatedPostNormBlock",
-           "ConvWindowAttention", "SinusoidalTokenEmbedding", "RMSNorm", "RotaryEmbedding", "GQAAttention"]
+           "ConvWindowAttention", "SinusoidalTokenEmbedding", "PositionalTokenEmbedding",
+           "Mamba2Mixer", "GatedMLP", "RoutedExperts", "SandwichNormBlock", "RMSNorm", "RotaryEmbedding", "GQAAttention"]

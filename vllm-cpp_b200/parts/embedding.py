@@ -84,14 +84,44 @@ class SinusoidalTokenEmbedding(TokenEmbedding):
         return out
 
 
+class PositionalTokenEmbedding(TokenEmbedding):
+    """x[t] = scale * E[id_t] + P[p_t]: the token's embedding times a constant, plus a learned vector for its position
+    (not scaled).  The table of positions bounds a request's length.
+
+    params: ``tensor``, ``position_tensor``, ``vocab_size``, ``hidden_size``, ``max_positions``, ``scale`` (default 1)."""
+    uses_positions = True
+
+    def __init__(self, params, prefix, build):
+        super().__init__(params, prefix, build)
+        self.pos_name = str(params["position_tensor"])
+        self.max_positions = int(params["max_positions"])
+        self.scale = float(params.get("scale", 1.0))
+        self.pos_table = None
+
+    def tensor_specs(self):
+        return super().tensor_specs() + [TensorSpec(self.pos_name, (self.max_positions, self.hidden))]
+
+    def bind(self, store):
+        super().bind(store)
+        self.pos_table = store.matrix(self.pos_name)
+
+    def forward(self, ids, n_tokens, status, positions=None):
+        if positions is None:
+            raise ValueError("this embedding adds a position vector: it needs the tokens' positions")
+        out = workspace.empty((n_tokens, self.hidden), torch.float32, ids.device)
+        ops.embed_scaled_pos(self.table, ids, positions, self.pos_table, self.scale, out, status)
+        return out
+
+
 class LMHead(Head):
     """params: ``tensor`` (checkpoint name of the head matrix, or None: the embedding table is the head),
-    ``vocab_size``, ``hidden_size``."""
+    ``vocab_size``, ``hidden_size``; optional ``softcap`` c > 0: logits <- c tanh(logits / c)."""
 
     def __init__(self, params, prefix, build):
         super().__init__(params, prefix, build)
         self.name = params.get("tensor")
         self.vocab, self.hidden = int(params["vocab_size"]), int(params["hidden_size"])
+        self.softcap = float(params.get("softcap") or 0.0)
         self.embedding = None
         self.weight = None
 
@@ -110,4 +140,7 @@ class LMHead(Head):
             self.weight = store.matrix(self.name)
 
     def forward(self, y, status=None):
-        return matmul_tn(y, self.weight, status, out_dtype=torch.float32, after_small_kernel=True)   # (after the last norm)
+        logits = matmul_tn(y, self.weight, status, out_dtype=torch.float32, after_small_kernel=True)   # (after the last norm)
+        if self.softcap > 0:
+            ops.softcap(logits, self.softcap)
+        return logits

@@ -99,7 +99,9 @@ class GatedPostNormBlock(Block):
 
     def forward(self, resid, pending, ctx, cache, writes=True):
         mark = getattr(ctx, "mark", lambda label: None)
-        if pending is not None:
+        if hasattr(pending, "add"):
+            pending.add(resid)
+        elif pending is not None:
             # a layer of another arrangement came before and left its last addition to this one
             resid.add_((pending.sum(0) if pending.dim() == 3 else pending).float())
         T, H = resid.shape

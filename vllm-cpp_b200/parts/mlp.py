@@ -101,3 +101,47 @@ class DenseMLP(FeedForward):
         act = workspace.empty((x.shape[0], self.inter), x.dtype, x.device)
         ops.bias_act(u, act, self.activation)
         return matmul_tn(act, self.w_down, ctx.status, out_dtype=torch.float32, allow_partials=True, after_small_kernel=True)
+
+
+class GatedMLP(FeedForward):
+    """down(act(gate(y) + b_g) * (up(y) + b_u)) + b_d: a feed-forward with a gate beside its up projection, any of the
+    activations of ``ops.ACTIVATIONS``, and optional biases on all three projections.  gate and up are one stacked
+    product (the gate's rows first); its sums, the biases and the activation are 32-bit.  The down projection's bias is
+    not added here: the part offers it as ``output_bias`` to whoever adds the result to the stream.
+
+    params: ``hidden_size``, ``intermediate_size``, ``activation`` (default "silu"), ``bias`` (default False), and the
+    tensor names under the prefix ``gate_tensor``, ``up_tensor``, ``down_tensor`` (default "gate", "up", "down"; a bias is
+    the matrix's name plus ".b")."""
+
+    def __init__(self, params, prefix, build):
+        super().__init__(params, prefix, build)
+        self.hidden = int(params["hidden_size"])
+        self.inter = int(params["intermediate_size"])
+        self.activation = str(params.get("activation", "silu"))
+        if self.activation not in ops.ACTIVATIONS:
+            raise ValueError(f"activation '{self.activation}' is not one of {sorted(ops.ACTIVATIONS)}")
+        self.has_bias = bool(params.get("bias", False))
+        self.names = tuple(prefix + str(params.get(k, d)) for k, d in (("gate_tensor", "gate"), ("up_tensor", "up"), ("down_tensor", "down")))
+        self.w_gate_up = self.w_down = self.bias = self.output_bias = None
+
+    def tensor_specs(self):
+        g, u, d = self.names
+        H, I = self.hidden, self.inter
+        specs = [TensorSpec(g, (I, H)), TensorSpec(u, (I, H)), TensorSpec(d, (H, I))]
+        if self.has_bias:
+            specs += [TensorSpec(g + ".b", (I,), "bias"), TensorSpec(u + ".b", (I,), "bias"), TensorSpec(d + ".b", (H,), "bias")]
+        return specs
+
+    def bind(self, store):
+        g, u, d = self.names
+        self.w_gate_up = store.matrices([g, u])
+        self.w_down = store.matrix(d)
+        if self.has_bias:
+            self.bias = torch.cat([store.vector(g + ".b").float(), store.vector(u + ".b").float()]).contiguous()
+            self.output_bias = store.vector(d + ".b").float().contiguous()
+
+    def forward(self, x, ctx):
+        gu = matmul_tn(x, self.w_gate_up, ctx.status, out_dtype=torch.float32, allow_partials=True, after_small_kernel=True)
+        act = workspace.empty((x.shape[0], self.inter), x.dtype, x.device)
+        ops.gated_act(gu, act, self.activation, self.bias)
+        return matmul_tn(act, self.w_down, ctx.status, out_dtype=torch.float32, allow_partials=True, after_small_kernel=True)

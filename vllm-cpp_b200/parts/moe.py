@@ -1,0 +1,90 @@
+"""A feed-forward of many small experts, of which a router picks a few per token, plus an optional shared expert
+that every token runs:
+
+    z = W_r y  (32-bit sums)          the `top` experts with the largest logits are chosen
+    w_e = sigmoid(z_e)                as it is ("sigmoid"), or the softmax over the chosen logits ("softmax")
+    out = sum_e expert_e(w_e y) + shared(y)        expert(v) = W_down act(W_up v), no biases
+
+The weight multiplies what the expert reads (``weight_on`` "input": the product w_e y is rounded to the compute dtype as
+any stored activation) or what it returns ("output").  Nothing asks the host which expert got how many tokens: the
+step's (token, choice) pairs are sorted by expert on the device into tiles of rows, each tile meeting one expert's
+weights, and the grids are laid out for the most tiles the step can need -- so a captured step replays the part.
+The router's rows ride on the shared expert's up projection (one product for both).
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import ops, workspace
+from ..weights.loader import TensorSpec
+from .base import FeedForward
+from .linear import matmul_tn
+
+
+class RoutedExperts(FeedForward):
+    """params: ``hidden_size``, ``num_experts``, ``top``, ``expert_size`` (an expert's hidden size), ``shared_size`` (0:
+    no shared expert), ``activation`` (default "relu2"), ``router_weights`` ("sigmoid" or "softmax"), ``weight_on``
+    ("input" or "output").  Tensors under the prefix: ``router`` [E, H]; ``e<i>.up`` [F, H], ``e<i>.down`` [H, F];
+    ``shared.up`` [Fs, H], ``shared.down`` [H, Fs]."""
+
+    def __init__(self, params, prefix, build):
+        super().__init__(params, prefix, build)
+        p = params
+        self.hidden, self.E, self.top = int(p["hidden_size"]), int(p["num_experts"]), int(p["top"])
+        self.ff, self.sff = int(p["expert_size"]), int(p.get("shared_size") or 0)
+        self.activation = str(p.get("activation", "relu2"))
+        self.router_weights = str(p.get("router_weights", "sigmoid"))
+        self.weight_on = str(p.get("weight_on", "input"))
+        if self.activation not in ops.ACTIVATIONS:
+            raise ValueError(f"activation '{self.activation}' is not one of {sorted(ops.ACTIVATIONS)}")
+        if self.router_weights not in ("sigmoid", "softmax") or self.weight_on not in ("input", "output"):
+            raise ValueError("router_weights is 'sigmoid' or 'softmax', weight_on 'input' or 'output'")
+        if not 1 <= self.top <= self.E:
+            raise ValueError(f"{self.top} of {self.E} experts")
+        self.w_side = self.w_up = self.w_down = self.w_shared_down = None
+
+    def tensor_specs(self):
+        p, H = self.prefix, self.hidden
+        specs = [TensorSpec(p + "router", (self.E, H))]
+        for e in range(self.E):
+            specs += [TensorSpec(f"{p}e{e}.up", (self.ff, H)), TensorSpec(f"{p}e{e}.down", (H, self.ff))]
+        if self.sff:
+            specs += [TensorSpec(p + "shared.up", (self.sff, H)), TensorSpec(p + "shared.down", (H, self.sff))]
+        return specs
+
+    def bind(self, store):
+        p = self.prefix
+        self.w_up = store.matrices([f"{p}e{e}.up" for e in range(self.E)]).view(self.E, self.ff, self.hidden)
+        self.w_down = store.matrices([f"{p}e{e}.down" for e in range(self.E)]).view(self.E, self.hidden, self.ff)
+        # the shared expert's up projection with the router's rows under it
+        self.w_side = store.matrices(([p + "shared.up"] if self.sff else []) + [p + "router"])
+        if self.sff:
+            self.w_shared_down = store.matrix(p + "shared.down")
+
+    def forward(self, x, ctx):
+        T, H = x.shape
+        dev, E, top, sff = x.device, self.E, self.top, self.sff
+        side = matmul_tn(x, self.w_side, ctx.status, out_dtype=torch.float32, allow_partials=True, after_small_kernel=True)
+        sel_e = workspace.empty((T, top), torch.int32, dev)
+        sel_w = workspace.empty((T, top), torch.float32, dev)
+        ops.moe_route(side[..., sff:], ctx.q_start, ctx.q_len, ctx.E, top, sel_e, sel_w,
+                      softmax_weights=self.router_weights == "softmax")
+        tiles = ops.moe_tiles_cap(T * top, E)
+        rows = tiles * ops.moe_tile_rows()
+        pos_of = workspace.empty((T * top,), torch.int32, dev)
+        src_of = workspace.empty((rows,), torch.int32, dev)
+        tile_expert = workspace.empty((tiles,), torch.int32, dev)
+        ops.moe_group(sel_e, E, tiles, pos_of, src_of, tile_expert)
+        on_input = self.weight_on == "input"
+        h1 = workspace.empty((rows, self.ff), x.dtype, dev)
+        ops.moe_gemm(x, self.w_up, tile_expert, h1, src_of=src_of, sel_w=sel_w if on_input else None, top=top, act=self.activation)
+        y = workspace.empty((rows, H), torch.float32, dev)
+        ops.moe_gemm(h1, self.w_down, tile_expert, y)
+        shared = None
+        if sff:
+            sa = workspace.empty((T, sff), x.dtype, dev)
+            ops.bias_act(side[..., :sff], sa, self.activation)
+            shared = matmul_tn(sa, self.w_shared_down, ctx.status, out_dtype=torch.float32, allow_partials=True, after_small_kernel=True)
+        out = workspace.empty((T, H), torch.float32, dev)
+        ops.moe_combine(y, pos_of, top, ctx.q_start, ctx.q_len, ctx.E, out, shared=shared, sel_w=None if on_input else sel_w)
+        return out

@@ -19,6 +19,7 @@ class RMSNorm(Norm):
         self.eps = float(params["eps"])
         self.name = self.prefix + str(params.get("name", "weight"))
         self.weight = None
+        self._gain32 = None
 
     def tensor_specs(self):
         return [TensorSpec(self.name, (self.size,), "vector")]
@@ -26,8 +27,19 @@ class RMSNorm(Norm):
     def bind(self, store):
         self.weight = store.vector(self.name)
 
+    def gain32(self):
+        """The gain as a 32-bit vector (made once): what the kernels that fuse this norm with other steps read."""
+        if self._gain32 is None:
+            self._gain32 = self.weight.float().contiguous()
+        return self._gain32
+
     def forward(self, resid, delta, rows=None):
         n = resid.shape[0] if rows is None else rows.numel()
         out = workspace.empty((n, self.size), self.build.compute_dtype, resid.device)
+        if delta is not None and not torch.is_tensor(delta):
+            # what the arrangement before left is more than a sum to add (a result still to be normed and scaled, say):
+            # it knows the kernel that does its addition and this norm in one pass
+            delta.add_then_norm(resid, self.gain32(), self.eps, out, rows)
+            return out
         ops.add_rmsnorm(resid, delta, self.weight, self.eps, out, rows)
         return out

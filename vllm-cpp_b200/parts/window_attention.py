@@ -9,7 +9,14 @@
 
 Query head h reads key/value head h // (heads / kv_heads); keys have ``head_dim`` lanes, values ``v_head_dim``.  The
 first ``keep_first`` keys of a request stay visible at their true distances.  Every option can be switched off (no
-bias, no convolution, no norm, no penalty, no window), so the part serves other designs of this family.
+bias, no convolution, no norm, no penalty, no window), so the part serves other designs of this family.  Further
+options, all off unless asked for:
+
+    ``whole_norm``      q <- g_q * q / rms(q) over all of a token's query lanes at once (before they are split into
+                        heads), with a gain per lane; the same for its key lanes (instead of the per-head unit norm)
+    ``softcap`` c       s <- c tanh(s / c) on the scaled score, before any distance term
+    ``slope_exponent`` a   slope_h (i - j) is taken off the score, slope_h = 2^(-a (h + 1) / heads)
+    ``sink``            a silent key of score 0 and no value in every softmax: w_j = exp(s_j) / (1 + sum_j exp(s_j))
 
 Per request the part keeps the keys and values in pages (given back as the window passes, except the pages of the
 kept first keys) and, for the convolution, the last taps - 1 rows of the stacked projection as a fixed-size state.
@@ -39,9 +46,10 @@ MMA_ATTENTION = os.environ.get("VLLM_CPP_B200_WINDOW_ATTN_MMA", "1") != "0"
 class ConvWindowAttention(Mixer):
     """params: ``hidden_size``, ``num_heads``, ``num_kv_heads``, ``head_dim``, ``v_head_dim`` (default head_dim),
     ``scale`` (default 1/sqrt(head_dim)), ``window`` (0: all keys), ``keep_first``, ``conv_taps`` (0: none), ``eps``,
-    ``unit_norm`` (default True), ``distance_penalty`` (default True), ``bias`` (default True).
+    ``unit_norm`` (default True), ``distance_penalty`` (default True), ``bias`` (default True); ``whole_norm``,
+    ``softcap``, ``slope_exponent``, ``sink`` (see above; default off).
     Tensors under ``<prefix>``: q [nh*hd, H], k [nkv*hd, H], v [nkv*vd, H], each with ``.b`` and ``.conv``
-    [channels, taps]; r1, r2 [nh] (a_h, b_h); o [H, nh*vd]."""
+    [channels, taps]; r1, r2 [nh] (a_h, b_h); q.norm [nh*hd], k.norm [nkv*hd] (whole_norm); o [H, nh*vd]."""
 
     def __init__(self, params, prefix, build):
         super().__init__(params, prefix, build)
@@ -57,6 +65,16 @@ class ConvWindowAttention(Mixer):
         self.unit_norm = bool(p.get("unit_norm", True))
         self.penalty = bool(p.get("distance_penalty", True))
         self.has_bias = bool(p.get("bias", True))
+        self.whole_norm = bool(p.get("whole_norm", False))
+        self.softcap = float(p.get("softcap") or 0.0)
+        self.slope_exponent = p.get("slope_exponent")
+        self.sink = bool(p.get("sink", False))
+        if self.whole_norm and (self.taps or self.has_bias):
+            raise ValueError("the norm over the whole projection comes without a bias and without a convolution")
+        if self.whole_norm:
+            self.unit_norm = False
+        if self.penalty and self.slope_exponent is not None:
+            raise ValueError("a logarithmic distance penalty and a slope at once")
         if self.nh % self.nkv:
             raise ValueError(f"{self.nh} query heads are not a multiple of {self.nkv} KV heads")
         for n in (self.hd, self.vd):
@@ -64,6 +82,7 @@ class ConvWindowAttention(Mixer):
                 raise ValueError(f"head size {n} is not supported: the kernels take 1 to 256")
         self.channels = self.nh * self.hd + self.nkv * (self.hd + self.vd)
         self.w_qkv = self.w_o = self.bias = self.conv_w = self.dist_a = self.dist_b = None
+        self.q_gain = self.k_gain = self.slope = None
 
     def cache_spec(self):
         kv = CacheSpec("kv", num_kv_heads=self.nkv, head_dim=self.hd, window=self.window, keep_first=self.keep_first,
@@ -82,6 +101,8 @@ class ConvWindowAttention(Mixer):
             specs += [TensorSpec(p + n + ".conv", (r, self.taps), "bias") for n, r in rows]
         if self.penalty:
             specs += [TensorSpec(p + "r1", (nh,), "positive"), TensorSpec(p + "r2", (nh,), "positive")]
+        if self.whole_norm:
+            specs += [TensorSpec(p + "q.norm", (nh * hd,), "vector"), TensorSpec(p + "k.norm", (nkv * hd,), "vector")]
         return specs
 
     def bind(self, store):
@@ -95,6 +116,12 @@ class ConvWindowAttention(Mixer):
             self.conv_w = torch.cat([f32("q.conv"), f32("k.conv"), f32("v.conv")], dim=0).contiguous()
         if self.penalty:
             self.dist_a, self.dist_b = f32("r1"), f32("r2")
+        if self.whole_norm:
+            self.q_gain, self.k_gain = f32("q.norm"), f32("k.norm")
+        if self.slope_exponent is not None:
+            # 2^(-a (h + 1) / heads): 64-bit on the host, rounded once
+            h = torch.arange(1, self.nh + 1, dtype=torch.float64)
+            self.slope = torch.pow(2.0, -float(self.slope_exponent) * h / self.nh).to(torch.float32).to(self.build.device)
 
     def forward(self, x, ctx, cache, writes=True):
         if not writes:
@@ -105,8 +132,12 @@ class ConvWindowAttention(Mixer):
         group = ctx.groups[kv.group]
         qkv = matmul_tn(x, self.w_qkv, ctx.status, out_dtype=torch.float32, allow_partials=True)
         q = workspace.empty((T, nh * hd), x.dtype, x.device)
-        ops.qkv_conv_norm_store(qkv, self.bias, self.conv_w, st, ctx.q_start, ctx.q_len, ctx.slots, group.slot_map, ctx.E,
-                                q, kv.pages, nh, nkv, hd, vd, self.eps, ctx.status, use_norm=self.unit_norm)
+        if self.whole_norm:
+            ops.qkv_wholenorm_store(qkv, self.q_gain, self.k_gain, self.eps, ctx.q_start, ctx.q_len, group.slot_map, ctx.E,
+                                    q, kv.pages, nh, nkv, hd, vd, ctx.status)
+        else:
+            ops.qkv_conv_norm_store(qkv, self.bias, self.conv_w, st, ctx.q_start, ctx.q_len, ctx.slots, group.slot_map, ctx.E,
+                                    q, kv.pages, nh, nkv, hd, vd, self.eps, ctx.status, use_norm=self.unit_norm)
         if self.taps > 1 and any(n > 1 for n in ctx.host_q_len):
             # (entries of one token were brought up to date by the kernel above)
             ops.conv_state_update(qkv, st, ctx.q_start, ctx.q_len, ctx.slots, ctx.E, bias=self.bias)
@@ -114,7 +145,10 @@ class ConvWindowAttention(Mixer):
         # no query reads more keys than the window and the kept first ones: no more key slices than those fill
         reach = self.window + self.keep_first if self.window else 0
         # bfloat16 with keys and values of 64 or 128 lanes: the tensor-core kernel; else the plain one
-        mma = MMA_ATTENTION and vd == hd and kv.pages.dim() == 5 and ops.attn_mma_supported(x.dtype, hd)
+        extras = dict(softcap=self.softcap, slope=self.slope, sink=self.sink)
+        has_extras = bool(self.softcap or self.slope is not None or self.sink)
+        mma = (MMA_ATTENTION and vd == hd and kv.pages.dim() == 5 and ops.attn_mma_supported(x.dtype, hd)
+               and not has_extras)
         dec_rows, span_rows = (MMA_DECODE_ROWS, MMA_SPAN_ROWS) if mma else (DECODE_ROWS, SPAN_ROWS)
         clustered = hd if mma and CLUSTER_MERGE and torch.cuda.is_available() else None
         plan = ctx.plan(("attention", nh, nkv, mma, clustered, reach),
@@ -134,7 +168,7 @@ class ConvWindowAttention(Mixer):
                              slice_counters=plan.slice_counters if S > 1 else None, dec_rows=plan.dec_rows, cluster=cluster,
                              **common)
             else:
-                ops.attn_window_bias(*args, plan.dec_items, plan.n_dec * S, dec_rows, part_o, part_ml, hd_v=vd, **common)
+                ops.attn_window_bias(*args, plan.dec_items, plan.n_dec * S, dec_rows, part_o, part_ml, hd_v=vd, **common, **extras)
                 if S > 1:
                     ops.attn_merge(part_o, part_ml, plan.dec_rows, out, plan.n_dec, nh, vd, S)
         if plan.n_span_items:
@@ -143,5 +177,5 @@ class ConvWindowAttention(Mixer):
             elif mma:
                 ops.attn_mma(*args, plan.span_items, plan.n_span_items, span_rows, None, None, **common)
             else:
-                ops.attn_window_bias(*args, plan.span_items, plan.n_span_items, span_rows, None, None, hd_v=vd, **common)
+                ops.attn_window_bias(*args, plan.span_items, plan.n_span_items, span_rows, None, None, hd_v=vd, **common, **extras)
         return matmul_tn(out, self.w_o, ctx.status, out_dtype=torch.float32, allow_partials=True)
