@@ -73,6 +73,21 @@ def sink_softmax(s):
     return e / (math.exp(-m) + e.sum())
 
 
+def attend_head(q, k, v, scale, cap, slope):
+    """One head: the last len(q) positions of a sequence of len(k) query all keys up to their own.  Capped scaled
+    scores less slope * distance, softmax with the silent sink.  q [n, d], k [L, d], v [L, dv] -> [n, dv]."""
+    n, L = q.shape[0], k.shape[0]
+    out = torch.zeros(n, v.shape[1], dtype=F64)
+    for r in range(n):
+        i = L - n + r
+        s = (k[:i + 1] @ q[r]) * scale
+        if cap:
+            s = capped(s, cap)
+        s = s - slope * (i - torch.arange(i + 1)).to(F64)
+        out[r] = sink_softmax(s) @ v[:i + 1]
+    return out
+
+
 def attention(x, w, pre, m, eps):
     """Grouped-query attention on full-projection-normed queries and keys, capped scores less a slope times the
     distance, causal, softmax with a silent sink.  x [T, W]."""
@@ -84,11 +99,7 @@ def attention(x, w, pre, m, eps):
     out = torch.zeros(T, H, dv, dtype=F64)
     for h in range(H):
         g = h // (H // G)
-        slope = head_slope(h, H)
-        for i in range(T):
-            j = torch.arange(i + 1)
-            s = capped((k[:i + 1, g] @ q[i, h]) * m["scale"], m["softcap"]) - slope * (i - j).to(F64)
-            out[i, h] = sink_softmax(s) @ v[:i + 1, g]
+        out[:, h] = attend_head(q[:, h], k[:, g], v[:, g], m["scale"], m.get("softcap"), head_slope(h, H))
     return out.reshape(T, H * dv) @ w[pre + "o"].T
 
 
@@ -105,19 +116,22 @@ def causal_conv(u, taps_weight, bias):
     return y
 
 
-def ssm_scan(xs, B, C, dt, a, D):
-    """Per head h (group g = h // (heads / groups)), from S = 0:  S <- exp(-a_h dt_t) S + dt_t B_t x_t^T,
-    y_t = S^T C_t + D_h x_t.   xs [T, heads, P], B and C [T, groups, N], dt [T, heads], a and D [heads]."""
+def ssm_scan(xs, B, C, dt, a, D, start=None):
+    """Per head h (group g = h // (heads / groups)), from S = 0 (or ``start`` [heads, N, P]):
+    S <- exp(-a_h dt_t) S + dt_t B_t x_t^T,  y_t = S^T C_t + D_h x_t.
+    xs [T, heads, P], B and C [T, groups, N], dt [T, heads], a and D [heads].  Returns y and the last states."""
     T, Hn, P = xs.shape
     Gn, N = B.shape[1], B.shape[2]
     y = torch.zeros(T, Hn, P, dtype=F64)
+    last = torch.zeros(Hn, N, P, dtype=F64)
     for h in range(Hn):
         g = h // (Hn // Gn)
-        S = torch.zeros(N, P, dtype=F64)
+        S = torch.zeros(N, P, dtype=F64) if start is None else start[h].clone()
         for t in range(T):
             S = math.exp(-float(a[h]) * float(dt[t, h])) * S + float(dt[t, h]) * torch.outer(B[t, g], xs[t, h])
             y[t, h] = S.T @ C[t, g] + D[h] * xs[t, h]
-    return y
+        last[h] = S
+    return y, last
 
 
 def grouped_rms_norm(y, gain, parts, eps):
@@ -137,7 +151,7 @@ def mamba2(x, w, pre, m, eps):
     B = xbc[:, inner:inner + Gn * N].reshape(T, Gn, N)
     C = xbc[:, inner + Gn * N:].reshape(T, Gn, N)
     dt = softplus(dt + w[pre + "dt_bias"])
-    y = ssm_scan(xs, B, C, dt, torch.exp(w[pre + "A_log"]), w[pre + "D"]).reshape(T, inner)
+    y = ssm_scan(xs, B, C, dt, torch.exp(w[pre + "A_log"]), w[pre + "D"])[0].reshape(T, inner)
     y = grouped_rms_norm(y * silu(z), w[pre + "norm"], m["norm_groups"], eps)
     return y @ w[pre + "o"].T
 
@@ -180,7 +194,7 @@ def forward(cfg, weights, tokens, keep_layers=False):
     """Logits [T, vocab] of one whole sequence (and, with keep_layers, the stream after every layer)."""
     w = {k: v.to(F64) for k, v in weights.items()}
     eps = cfg["norm"]["eps"]
-    x = embed(tokens, w["embed"], w["pos"], cfg["embedding"]["scale"])
+    x = embed(tokens, w["embed"], w["pos"], (cfg.get("embedding") or {}).get("scale", 1.0))
     after = []
     for i, layer in enumerate(cfg["layers"]):
         p = f"l{i}."
@@ -193,7 +207,8 @@ def forward(cfg, weights, tokens, keep_layers=False):
             x = x + rms_norm(d, w[p + "norm2b"], eps) * w[p + "ls2"]
         after.append(x.clone())
     logits = rms_norm(x, w["final.norm"], eps) @ w["head"].T
-    logits = capped(logits, cfg["logit_softcap"])
+    if cfg.get("logit_softcap"):
+        logits = capped(logits, cfg["logit_softcap"])
     return (logits, after) if keep_layers else logits
 
 

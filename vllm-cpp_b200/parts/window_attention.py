@@ -41,6 +41,8 @@ from .linear import matmul_tn
 
 # 0 keeps every step on the plain attention kernel (comparison runs, tests)
 MMA_ATTENTION = os.environ.get("VLLM_CPP_B200_WINDOW_ATTN_MMA", "1") != "0"
+# whether the tensor-core kernels take the cap, the slope and the sink (else steps with them run on the plain kernel)
+EXTRAS_ON_TENSOR_CORES = False
 
 
 class ConvWindowAttention(Mixer):
@@ -148,7 +150,7 @@ class ConvWindowAttention(Mixer):
         extras = dict(softcap=self.softcap, slope=self.slope, sink=self.sink)
         has_extras = bool(self.softcap or self.slope is not None or self.sink)
         mma = (MMA_ATTENTION and vd == hd and kv.pages.dim() == 5 and ops.attn_mma_supported(x.dtype, hd)
-               and not has_extras)
+               and (EXTRAS_ON_TENSOR_CORES or not has_extras))
         dec_rows, span_rows = (MMA_DECODE_ROWS, MMA_SPAN_ROWS) if mma else (DECODE_ROWS, SPAN_ROWS)
         clustered = hd if mma and CLUSTER_MERGE and torch.cuda.is_available() else None
         plan = ctx.plan(("attention", nh, nkv, mma, clustered, reach),
