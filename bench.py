@@ -1,7 +1,7 @@
 #!/usr/bin/env python3
 """Benchmark of the engine on one B200.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--workloads all|headline|14b|4b|rimopel] [--impl reference]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--workloads all|headline|14b|4b|rimopel|nagavik] [--impl reference]
 
 Headline: decode tokens/s of the Qwen3-8B layer sizes (the baseline's third configuration) at batch 8 and context
 4,096, the median of K device-timed steps after W warm-up steps; beside it batch 1 and 64, batch 8 at context 2,176
@@ -446,42 +446,23 @@ RIMOPEL_SIZES = {
 }
 
 
-def run_rimopel(args, pk, clocks, windows):
-    """Prefill (one prompt of 2,048 tokens in one step) and decode (batch 8 behind a context of 4,096 tokens, captured
-    steps) of Rimopel at real layer sizes, beside Qwen3 with the same width, heads, window on every layer, layer count and
-    feed-forward parameter count: tokens/s, the fraction of the measured roofline, and the time per group of kernels."""
+def run_beside(args, pk, clocks, windows, workload, sizes, configs, numbers):
+    """Prefill (one prompt of 2,048 tokens in one step) and decode (a batch behind a context of 4,096 tokens, captured
+    steps) of a design at real layer sizes beside Qwen3 at equal size: tokens/s, the fraction of the measured roofline
+    (each model's own work counted), and the time per group of kernels.  ``configs(z)``: name -> configuration;
+    ``numbers(z, name)``: weight_bytes and per-request cache_bytes a decode step reads, and the prefill's flops."""
     import numpy as np
     import torch
-    from vllm_cpp_b200 import EngineConfig, LLM, Qwen3Config, ops
-    from vllm_cpp_b200.config.rimopel import RimopelConfig, RimopelLayer, RimopelMixer
+    from vllm_cpp_b200 import EngineConfig, LLM, ops
     from vllm_cpp_b200.engine.step import StepEntry
     from vllm_cpp_b200.runtime import runtime
 
     rt = runtime()
     rng = np.random.default_rng(0)
     B, context, T = args.batch, args.context, PREFILL_TOKENS
-    out = {"workload": "rimopel_beside_qwen3", "batch": B, "context": context, "prefill_tokens": T, "peaks": pk["source"],
+    out = {"workload": workload, "batch": B, "context": context, "prefill_tokens": T, "peaks": pk["source"],
            "data": "synthetic (random weights, uniform random token ids, random cache contents for the held context)",
            "l2": "inputs (over 1 GB of weights) larger than L2", "timing": "median of steps, CUDA events", "sizes": {}}
-
-    def configs(z):
-        mixer = RimopelMixer(heads=z["heads"], kv_heads=z["kv_heads"], dim=z["dim"], vdim=z["dim"], scale=z["dim"] ** -0.5, conv=3,
-                             window=z["window"], keep_first=4)
-        rim = RimopelConfig(vocab=z["vocab"], width=z["width"], norm_eps=1e-5, canon_taps=3, max_positions=context + 4096,
-                            layers=tuple(RimopelLayer("attention", mixer, "dense", z["ff"]) for _ in range(z["layers"])))
-        qwen = Qwen3Config(vocab_size=z["vocab"], hidden_size=z["width"], intermediate_size=z["swiglu"], num_hidden_layers=z["layers"],
-                           num_attention_heads=z["heads"], num_key_value_heads=z["kv_heads"], head_dim=z["dim"],
-                           max_position_embeddings=context + 4096, rms_norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=False,
-                           sliding_window=z["window"], layer_types=("sliding_attention",) * z["layers"])
-        return {"rimopel": rim, "qwen3": qwen}
-
-    def numbers(z, name):
-        W, H, G, d, L, V = z["width"], z["heads"], z["kv_heads"], z["dim"], z["layers"], z["vocab"]
-        attn = (H + 2 * G) * d * W + W * H * d
-        layer = attn + (2 * z["ff"] * W + 2 * W * W if name == "rimopel" else 3 * z["swiglu"] * W)
-        keys = min(context, z["window"])
-        return dict(weight_bytes=2 * (L * layer + V * W), kv_bytes=L * 2 * G * d * 2 * keys,
-                    prefill_flops=2.0 * T * L * layer + 2.0 * V * W + L * 4.0 * H * d * sum(min(i + 1, z["window"]) for i in range(T)))
 
     def measure(cfg, z, name, profile):
         per_req = -(-(context + args.steps + args.warmup + 8) // 64) * 64
@@ -490,9 +471,9 @@ def run_rimopel(args, pk, clocks, windows):
                                                                 max_step_tokens=T, max_model_len=context + 4096, profile=profile))
         runner = llm.runner
         V = z["vocab"]
-        for t in runner.cache.tensors:
+        for g, t in zip(runner.layout.groups, runner.cache.tensors):
             for i in range(t.shape[0]):
-                t[i].normal_(0, 1)
+                t[i].normal_(0, 1 if g.paged else 0.01)
         n_groups = len(runner.layout.paged)
 
         def fresh():
@@ -551,12 +532,14 @@ def run_rimopel(args, pk, clocks, windows):
         res.update(prefill_ms=pf_ms, prefill_tokens_per_s=T * 1000.0 / pf_ms,
                    prefill_frac_of_bf16_peak=n["prefill_flops"] / (pf_ms * 1e-3) / (pk["bf16_tflops"] * 1e12),
                    decode_ms=dec_ms, decode_tokens_per_s=B * 1000.0 / dec_ms,
-                   decode_frac_of_hbm_peak=(n["weight_bytes"] + B * n["kv_bytes"]) / (dec_ms * 1e-3) / 1e9 / pk["hbm_gbs"])
+                   decode_frac_of_hbm_peak=(n["weight_bytes"] + B * n["cache_bytes"]) / (dec_ms * 1e-3) / 1e9 / pk["hbm_gbs"])
         del llm, runner
         release()
         return res
 
-    for size, z in RIMOPEL_SIZES.items():
+    for size, z in sizes.items():
+        if args.size and size != args.size:
+            continue
         out["sizes"][size] = {"config": z}
         for name, cfg in configs(z).items():
             r = measure(cfg, z, name, profile=False)
@@ -565,6 +548,93 @@ def run_rimopel(args, pk, clocks, windows):
             r["prefill_launches"] = p["prefill_launches"]
             out["sizes"][size][name] = r
     return out
+
+
+def run_rimopel(args, pk, clocks, windows):
+    """Rimopel at real layer sizes beside Qwen3 with the same width, heads, window on every layer, layer count and
+    feed-forward parameter count (see run_beside)."""
+    from vllm_cpp_b200 import Qwen3Config
+    from vllm_cpp_b200.config.rimopel import RimopelConfig, RimopelLayer, RimopelMixer
+    context, T = args.context, PREFILL_TOKENS
+
+    def configs(z):
+        mixer = RimopelMixer(heads=z["heads"], kv_heads=z["kv_heads"], dim=z["dim"], vdim=z["dim"], scale=z["dim"] ** -0.5, conv=3,
+                             window=z["window"], keep_first=4)
+        rim = RimopelConfig(vocab=z["vocab"], width=z["width"], norm_eps=1e-5, canon_taps=3, max_positions=context + 4096,
+                            layers=tuple(RimopelLayer("attention", mixer, "dense", z["ff"]) for _ in range(z["layers"])))
+        qwen = Qwen3Config(vocab_size=z["vocab"], hidden_size=z["width"], intermediate_size=z["swiglu"], num_hidden_layers=z["layers"],
+                           num_attention_heads=z["heads"], num_key_value_heads=z["kv_heads"], head_dim=z["dim"],
+                           max_position_embeddings=context + 4096, rms_norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=False,
+                           sliding_window=z["window"], layer_types=("sliding_attention",) * z["layers"])
+        return {"rimopel": rim, "qwen3": qwen}
+
+    def numbers(z, name):
+        W, H, G, d, L, V = z["width"], z["heads"], z["kv_heads"], z["dim"], z["layers"], z["vocab"]
+        attn = (H + 2 * G) * d * W + W * H * d
+        layer = attn + (2 * z["ff"] * W + 2 * W * W if name == "rimopel" else 3 * z["swiglu"] * W)
+        keys = min(context, z["window"])
+        return dict(weight_bytes=2 * (L * layer + V * W), cache_bytes=L * 2 * G * d * 2 * keys,
+                    prefill_flops=2.0 * T * L * layer + 2.0 * V * W + L * 4.0 * H * d * sum(min(i + 1, z["window"]) for i in range(T)))
+
+    return run_beside(args, pk, clocks, windows, "rimopel_beside_qwen3", RIMOPEL_SIZES, configs, numbers)
+
+
+# Nagavik at real layer sizes: two recurrent layers, then one attention layer, and so on; every layer with routed experts
+# (two of sixteen) and a shared expert.  Qwen3 beside it has the same width, heads, layer count (attention on every
+# layer) and as many feed-forward parameters per token as Nagavik has active ones (three matrices of width x ff).
+NAGAVIK_SIZES = {
+    "w2048": dict(width=2048, heads=16, kv_heads=4, dim=128, ssm_heads=64, ssm_vdim=64, state=128, groups=8, experts=16, top=2,
+                  ff=2048, shared=2048, swiglu=4096, layers=12, vocab=32768),
+    "w4096": dict(width=4096, heads=32, kv_heads=8, dim=128, ssm_heads=128, ssm_vdim=64, state=128, groups=8, experts=16, top=2,
+                  ff=4096, shared=4096, swiglu=8192, layers=8, vocab=32768),
+}
+
+
+def run_nagavik(args, pk, clocks, windows):
+    """Nagavik at real layer sizes beside Qwen3 at equal size (see NAGAVIK_SIZES and run_beside)."""
+    from vllm_cpp_b200 import Qwen3Config
+    from vllm_cpp_b200.config.nagavik import NagavikAttention, NagavikConfig, NagavikLayer, NagavikMamba2, NagavikMlp
+    context, T, B = args.context, PREFILL_TOKENS, args.batch
+
+    def kinds(z):
+        return ["attention" if i % 3 == 2 else "mamba2" for i in range(z["layers"])]
+
+    def configs(z):
+        attn = NagavikAttention(heads=z["heads"], kv_heads=z["kv_heads"], dim=z["dim"], vdim=z["dim"], scale=z["dim"] ** -0.5, softcap=50.0)
+        ssm = NagavikMamba2(heads=z["ssm_heads"], vdim=z["ssm_vdim"], state=z["state"], groups=z["groups"], conv=4, norm_groups=z["groups"])
+        mlp = NagavikMlp("moe", ff=z["ff"], experts=z["experts"], top=z["top"], shared_ff=z["shared"])
+        nag = NagavikConfig(vocab=z["vocab"], width=z["width"], max_positions=context + 4096, norm_eps=1e-5, embedding_scale=1.0,
+                            logit_softcap=30.0,
+                            layers=tuple(NagavikLayer(k, attn if k == "attention" else ssm, mlp) for k in kinds(z)))
+        qwen = Qwen3Config(vocab_size=z["vocab"], hidden_size=z["width"], intermediate_size=z["swiglu"], num_hidden_layers=z["layers"],
+                           num_attention_heads=z["heads"], num_key_value_heads=z["kv_heads"], head_dim=z["dim"],
+                           max_position_embeddings=context + 4096, rms_norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=False)
+        return {"nagavik": nag, "qwen3": qwen}
+
+    def numbers(z, name):
+        W, H, G, d, L, V = z["width"], z["heads"], z["kv_heads"], z["dim"], z["layers"], z["vocab"]
+        attn_w = (H + 2 * G) * d * W + W * H * d
+        attn_flops = 4.0 * H * d * sum(i + 1 for i in range(T))
+        if name == "qwen3":
+            layer = attn_w + 3 * z["swiglu"] * W
+            return dict(weight_bytes=2 * (L * layer + V * W), cache_bytes=L * 2 * G * d * 2 * context,
+                        prefill_flops=2.0 * T * L * layer + 2.0 * V * W + L * attn_flops)
+        n_attn = kinds(z).count("attention")
+        n_ssm = L - n_attn
+        inner, gn = z["ssm_heads"] * z["ssm_vdim"], z["groups"] * z["state"]
+        ssm_w = (2 * inner + 2 * gn + z["ssm_heads"]) * W + W * inner
+        expert = 2 * z["ff"] * W
+        ff_active = z["top"] * expert + 2 * z["shared"] * W + z["experts"] * W
+        # experts a decode step reads: the distinct ones B tokens choose, in expectation
+        distinct = z["experts"] * (1.0 - (1.0 - z["top"] / z["experts"]) ** B)
+        ff_read = distinct * expert + 2 * z["shared"] * W + z["experts"] * W
+        state_bytes = 2 * 4 * inner * z["state"]       # read and written, 32-bit
+        return dict(weight_bytes=2 * (n_attn * attn_w + n_ssm * ssm_w + L * ff_read + V * W),
+                    cache_bytes=n_attn * 2 * G * d * 2 * context + n_ssm * state_bytes,
+                    prefill_flops=2.0 * T * (n_attn * attn_w + n_ssm * ssm_w + L * ff_active) + 2.0 * V * W + n_attn * attn_flops
+                                  + n_ssm * 6.0 * T * inner * z["state"])
+
+    return run_beside(args, pk, clocks, windows, "nagavik_beside_qwen3", NAGAVIK_SIZES, configs, numbers)
 
 
 def main():
@@ -578,9 +648,10 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=CONTEXT)
     ap.add_argument("--impl", default="ours")
-    ap.add_argument("--workloads", default="all", choices=["all", "headline", "14b", "4b", "rimopel"],
-                    help="headline: the 8B numbers only; 14b / 4b: that workload alone (prints its own JSON line); rimopel: "
-                         "Rimopel at real layer sizes beside Qwen3 at equal size, prefill and decode (its own JSON line)")
+    ap.add_argument("--workloads", default="all", choices=["all", "headline", "14b", "4b", "rimopel", "nagavik"],
+                    help="headline: the 8B numbers only; 14b / 4b: that workload alone (prints its own JSON line); rimopel, "
+                         "nagavik: that design at real layer sizes beside Qwen3 at equal size, prefill and decode (its own JSON line)")
+    ap.add_argument("--size", default="", help="rimopel, nagavik: one of the workload's sizes only (w2048, w4096)")
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch (for profiling runs)")
     ap.add_argument("--no-graphs", action="store_true", help="launch decode steps kernel by kernel (for profiling runs)")
     ap.add_argument("--mode", default="all", choices=["all", "decode", "prefill"], help="what to run (profiling runs)")
@@ -602,8 +673,8 @@ def main():
     clocks.start()
     windows = []
     try:
-        if args.workloads in ("14b", "4b", "rimopel"):
-            out = {"14b": run_14b, "4b": run_4b, "rimopel": run_rimopel}[args.workloads](args, pk, clocks, windows)
+        if args.workloads in ("14b", "4b", "rimopel", "nagavik"):
+            out = {"14b": run_14b, "4b": run_4b, "rimopel": run_rimopel, "nagavik": run_nagavik}[args.workloads](args, pk, clocks, windows)
             out["clocks"] = clocks.summary(windows)
             print(json.dumps(out))
             return 0

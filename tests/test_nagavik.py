@@ -637,10 +637,24 @@ def test_gate_then_norm_in_parts(C, parts, S, dtype):
 
 
 @gpu
+@pytest.mark.parametrize("tile_rows", [16, 32, 64, 128, 256])
+@pytest.mark.parametrize("T,H,E,top,ff,sff,on_input", [(1, 16, 4, 1, 8, 0, True), (37, 48, 5, 2, 24, 12, True), (300, 64, 3, 3, 16, 40, True),
+                                                       (64, 56, 70, 4, 200, 0, False), (9, 256, 12, 1, 96, 96, True), (700, 128, 6, 2, 136, 0, True)])
+def test_routed_experts_on_tensor_cores(tile_rows, T, H, E, top, ff, sff, on_input):
+    """The same through the gathered rows and the grouped tcgen05 product, at every tile size: experts of fewer rows than
+    a block of 128 features (the next expert's rows in the same weight tile must not leak), of more, of no multiple."""
+    check_routed_experts(torch.bfloat16, T, H, E, top, ff, sff, on_input, tile_rows)
+
+
+@gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("T,H,E,top,ff,sff,on_input", [(1, 16, 4, 1, 8, 0, True), (37, 48, 5, 2, 24, 12, True), (150, 64, 3, 3, 16, 40, True),
                                                        (64, 50, 70, 4, 9, 0, False), (9, 32, 12, 1, 96, 96, True)])
 def test_routed_experts(dtype, T, H, E, top, ff, sff, on_input):
+    check_routed_experts(dtype, T, H, E, top, ff, sff, on_input, None)
+
+
+def check_routed_experts(dtype, T, H, E, top, ff, sff, on_input, tile_rows):
     """Router, sorting into tiles, the experts' two products and the sum per token against the plain feed-forward; experts
     that no token chose, more experts than tokens, every expert chosen by every token; rows of padding route nowhere."""
     from vllm_cpp_b200 import ops
@@ -659,11 +673,12 @@ def test_routed_experts(dtype, T, H, E, top, ff, sff, on_input):
     order = torch.topk(logits[:T], top, dim=1)
     assert torch.equal(sel_e.cpu()[:T].long(), order.indices) and bool((sel_e[T:] == -1).all())
     torch.testing.assert_close(sel_w.double().cpu()[:T], torch.sigmoid(order.values), atol=1e-5, rtol=1e-5)
-    tiles, BM = ops.moe_tiles_cap((T + 2) * top, E), ops.moe_tile_rows()
+    BM = tile_rows or ops.moe_tile_rows()
+    tiles = ops.moe_tiles_cap((T + 2) * top, E, BM)
     pos_of = torch.empty((T + 2) * top, dtype=torch.int32, device=dev())
     src_of = torch.empty(tiles * BM, dtype=torch.int32, device=dev())
     tile_expert = torch.empty(tiles, dtype=torch.int32, device=dev())
-    ops.moe_group(sel_e, E, tiles, pos_of, src_of, tile_expert)
+    ops.moe_group(sel_e, E, tiles, pos_of, src_of, tile_expert, BM)
     po, so, te, se = pos_of.cpu().tolist(), src_of.cpu().tolist(), tile_expert.cpu().tolist(), sel_e.cpu().view(-1).tolist()
     for a, pos in enumerate(po):
         if se[a] < 0:
@@ -675,9 +690,19 @@ def test_routed_experts(dtype, T, H, E, top, ff, sff, on_input):
     w_up = torch.stack([w[f"e{e}.up"] for e in range(E)]).to(dtype).to(dev())
     w_down = torch.stack([w[f"e{e}.down"] for e in range(E)]).to(dtype).to(dev())
     h1 = torch.full((tiles * BM, ff), float("nan"), device=dev(), dtype=dtype)
-    ops.moe_gemm(xd, w_up, tile_expert, h1, src_of=src_of, sel_w=sel_w if on_input else None, top=top, act="relu2")
     y = torch.full((tiles * BM, H), float("nan"), device=dev())
-    ops.moe_gemm(h1, w_down, tile_expert, y)
+    if tile_rows:
+        # the tensor-core products: the rows gathered and weighted in sorted order first
+        assert ops.gemm_grouped_ok(xd, w_up) and ops.gemm_grouped_ok(xd, w_down)
+        xs = torch.full((tiles * BM, H), float("nan"), device=dev(), dtype=dtype)
+        status = torch.zeros(1, dtype=torch.int32, device=dev())
+        ops.moe_gather(xd, src_of, sel_w if on_input else None, top, xs)
+        ops.gemm_bf16_grouped(w_up, xs, tile_expert, BM, h1, status, act="relu2")
+        ops.gemm_bf16_grouped(w_down, h1, tile_expert, BM, y, status)
+        assert status.item() == 0
+    else:
+        ops.moe_gemm(xd, w_up, tile_expert, h1, src_of=src_of, sel_w=sel_w if on_input else None, top=top, act="relu2")
+        ops.moe_gemm(h1, w_down, tile_expert, y)
     shared = torch.randn(T + 2, H, generator=g, dtype=F64) if sff else None
     out = torch.full((T + 2, H), 4.0, device=dev())
     ops.moe_combine(y, pos_of, top, qs, ql, 3, out, shared=None if shared is None else partial_sums(shared, 2, g),

@@ -126,7 +126,20 @@ struct GemmArgs {
     int* status;
     QkvEpilogue qe;
     int pf_tiles, pf_delay_ns;   // weight tiles asked into L2 beyond the first ring, that long after the block's start (0: none)
+    // A product over groups of tokens that each meet another matrix (experts): W is the groups' matrices stacked,
+    // group_rows features each; the tokens lie sorted by group in tiles of BN rows, tile i belonging to group
+    // tile_group[i] (-1: an empty tile, skipped).  M is then group_rows and the output has group_rows columns.
+    // Null: an ordinary product.
+    const int* tile_group;
+    int group_rows;
+    int act;                  // applied to the sums before they are stored: 0 none, 3 the square of ReLU, 2 SiLU
 };
+
+__device__ __forceinline__ float gemm_act(float x, int act) {
+    if (act == 3) { const float r = fmaxf(x, 0.f); return r * r; }
+    if (act == 2) return x / (1.f + __expf(-x));
+    return x;
+}
 
 // MT = 128-feature tiles per work unit that share one token tile (2 halves the bytes that cross L2 per flop);
 // ACC = accumulator buffers in TMEM (2: the epilogue of one unit overlaps the MMAs of the next).
@@ -337,8 +350,9 @@ __global__ __launch_bounds__(NTHREADS, 1) void gemm_bf16_tn_kernel(const __grid_
     tc_fence_after();
     const uint32_t tmem_base = *tmem_holder;
 
-    // unit -> (first feature, first token, first k-block, k-blocks)
-    auto unit_at = [&](int u, int& m0, int& n0, int& kb0, int& nkb, int& z) {
+    // unit -> (first feature, first token, first k-block, k-blocks); in a grouped product also the first row of the
+    // tile's group in the stacked matrix (m0 counts from there on; no k-blocks: an empty tile, every role skips it)
+    auto unit_at = [&](int u, int& m0, int& n0, int& kb0, int& nkb, int& z, int& mo) {
         z = u / (m_tiles * n_tiles);
         int mi, ni;
         tile_of(u % (m_tiles * n_tiles), m_tiles, n_tiles, mi, ni);
@@ -346,6 +360,12 @@ __global__ __launch_bounds__(NTHREADS, 1) void gemm_bf16_tn_kernel(const __grid_
         m0 = mi * unit_rows;
         kb0 = z * g.kb_per_split;
         nkb = min(total_kb, kb0 + g.kb_per_split) - kb0;
+        mo = 0;
+        if (g.tile_group != nullptr) {
+            const int grp = g.tile_group[ni];
+            if (grp < 0) nkb = 0;
+            else mo = grp * g.group_rows;
+        }
     };
 
     if (warp == 0) {
@@ -358,9 +378,9 @@ __global__ __launch_bounds__(NTHREADS, 1) void gemm_bf16_tn_kernel(const __grid_
             // flight while that kernel drains.  The activation tiles of those stages follow after the wait.
             int early = 0;
             {
-                int m0, n0, kb0, nkb, z;
-                if ((int)blockIdx.x < units) {
-                    unit_at(blockIdx.x, m0, n0, kb0, nkb, z);
+                int m0, n0, kb0, nkb, z, mo;
+                if ((int)blockIdx.x < units && g.tile_group == nullptr) {   // (which group a tile has is known only after the wait)
+                    unit_at(blockIdx.x, m0, n0, kb0, nkb, z, mo);
                     early = min(nkb, STAGES);
                     for (int i = 0; i < early; ++i) {
                         mbar_expect_tx(full_bar(i), L::STAGE_BYTES);
@@ -382,7 +402,7 @@ __global__ __launch_bounds__(NTHREADS, 1) void gemm_bf16_tn_kernel(const __grid_
                         // the k-blocks after the ring, on into this block's next units
                         int left = g.pf_tiles, i = early;
                         for (int u = blockIdx.x; u < units && left > 0; u += gridDim.x) {
-                            unit_at(u, m0, n0, kb0, nkb, z);
+                            unit_at(u, m0, n0, kb0, nkb, z, mo);
                             for (; i < nkb && left > 0; ++i, --left)
 #pragma unroll
                                 for (int mt = 0; mt < MT; ++mt) tma_prefetch_2d(&map_w, (kb0 + i) * BK, m0 + mt * BM);
@@ -394,8 +414,8 @@ __global__ __launch_bounds__(NTHREADS, 1) void gemm_bf16_tn_kernel(const __grid_
             pdl_wait();
             tl_mark(VCB_TL_GEMM, 1);
             for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
-                int m0, n0, kb0, nkb, z;
-                unit_at(u, m0, n0, kb0, nkb, z);
+                int m0, n0, kb0, nkb, z, mo;
+                unit_at(u, m0, n0, kb0, nkb, z, mo);
                 for (int i = 0; i < nkb; ++i, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
@@ -409,7 +429,7 @@ __global__ __launch_bounds__(NTHREADS, 1) void gemm_bf16_tn_kernel(const __grid_
 #pragma unroll
                     for (int mt = 0; mt < MT; ++mt)
                         tma_load_2d(a_dst + mt * L::A_BYTES, &map_w, full_bar(s), (kb0 + i) * BK,
-                                    m0 + mt * BM);
+                                    mo + m0 + mt * BM);
                     tma_load_2d(a_dst + MT * L::A_BYTES, &map_x, full_bar(s), (kb0 + i) * BK, n0);
                     armed = it + 1;
                 }
@@ -428,11 +448,14 @@ __global__ __launch_bounds__(NTHREADS, 1) void gemm_bf16_tn_kernel(const __grid_
             constexpr uint32_t idesc = instr_desc(BN);
             int it = 0, j = 0;
             bool ok = true;
-            for (int u = blockIdx.x; u < units && ok; u += gridDim.x, ++j) {
-                int m0, n0, kb0, nkb, z;
-                unit_at(u, m0, n0, kb0, nkb, z);
+            if (g.tile_group != nullptr) pdl_wait();     // (the tiles' groups come from a kernel before this one)
+            for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
+                int m0, n0, kb0, nkb, z, mo;
+                unit_at(u, m0, n0, kb0, nkb, z, mo);
+                if (nkb == 0) continue;
                 const int a = j % ACC;
-                ok = mbar_wait(acc_empty_bar(a), ((j / ACC) & 1) ^ 1u, abort_flag, g.status);   // drained by the epilogue
+                ++j;
+                ok = mbar_wait(acc_empty_bar(a), (((j - 1) / ACC) & 1) ^ 1u, abort_flag, g.status);   // drained by the epilogue
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t tmem_d = tmem_base + a * (MT * ACC_COLS);
@@ -460,11 +483,14 @@ __global__ __launch_bounds__(NTHREADS, 1) void gemm_bf16_tn_kernel(const __grid_
         // ---- epilogue: warps 2..5 own TMEM lane quarters 2, 3, 0, 1 ----
         const int q = warp & 3;
         int j = 0;
-        for (int u = blockIdx.x; u < units; u += gridDim.x, ++j) {
-            int m0, n0, kb0, nkb, z;
-            unit_at(u, m0, n0, kb0, nkb, z);
+        if (g.tile_group != nullptr) pdl_wait();
+        for (int u = blockIdx.x; u < units; u += gridDim.x) {
+            int m0, n0, kb0, nkb, z, mo;
+            unit_at(u, m0, n0, kb0, nkb, z, mo);
+            if (nkb == 0) continue;
             const int a = j % ACC;
-            if (!mbar_wait(acc_full_bar(a), (j / ACC) & 1, abort_flag, g.status)) break;
+            ++j;
+            if (!mbar_wait(acc_full_bar(a), ((j - 1) / ACC) & 1, abort_flag, g.status)) break;
             tc_fence_after();
             const uint32_t tmem_d = tmem_base + a * (MT * ACC_COLS);
             const size_t zoff = (size_t)z * g.split_stride;
@@ -499,13 +525,13 @@ __global__ __launch_bounds__(NTHREADS, 1) void gemm_bf16_tn_kernel(const __grid_
                         float* o = reinterpret_cast<float*>(g.out) + zoff;
 #pragma unroll
                         for (int jj = 0; jj < CHUNK; ++jj)
-                            if (n0 + c0 + jj < g.N) o[(size_t)(n0 + c0 + jj) * g.ldc + m] = __uint_as_float(v[jj / 16][jj % 16]);
+                            if (n0 + c0 + jj < g.N) o[(size_t)(n0 + c0 + jj) * g.ldc + m] = gemm_act(__uint_as_float(v[jj / 16][jj % 16]), g.act);
                     } else {
                         __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(g.out) + zoff;
 #pragma unroll
                         for (int jj = 0; jj < CHUNK; ++jj)
                             if (n0 + c0 + jj < g.N)
-                                o[(size_t)(n0 + c0 + jj) * g.ldc + m] = __float2bfloat16_rn(__uint_as_float(v[jj / 16][jj % 16]));
+                                o[(size_t)(n0 + c0 + jj) * g.ldc + m] = __float2bfloat16_rn(gemm_act(__uint_as_float(v[jj / 16][jj % 16]), g.act));
                     }
                 }
             }
@@ -743,13 +769,13 @@ __global__ __launch_bounds__(NTHREADS, 1) void gemm_bf16_tn_pair_kernel(const __
                         float* o = reinterpret_cast<float*>(g.out) + zoff;
 #pragma unroll
                         for (int jj = 0; jj < CHUNK; ++jj)
-                            if (n0 + c0 + jj < g.N) o[(size_t)(n0 + c0 + jj) * g.ldc + m] = __uint_as_float(v[jj / 16][jj % 16]);
+                            if (n0 + c0 + jj < g.N) o[(size_t)(n0 + c0 + jj) * g.ldc + m] = gemm_act(__uint_as_float(v[jj / 16][jj % 16]), g.act);
                     } else {
                         __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(g.out) + zoff;
 #pragma unroll
                         for (int jj = 0; jj < CHUNK; ++jj)
                             if (n0 + c0 + jj < g.N)
-                                o[(size_t)(n0 + c0 + jj) * g.ldc + m] = __float2bfloat16_rn(__uint_as_float(v[jj / 16][jj % 16]));
+                                o[(size_t)(n0 + c0 + jj) * g.ldc + m] = __float2bfloat16_rn(gemm_act(__uint_as_float(v[jj / 16][jj % 16]), g.act));
                     }
                 }
             }
@@ -1074,6 +1100,38 @@ VCB_API int vcb_gemm_bf16_tn_shape(const void* W, const void* X, void* out, int 
     if ((flags & VCB_GEMM_AFTER_SMALL_KERNEL) && N <= 16 && vcb_pdl_enabled()) pf_settings(&g.pf_tiles, &g.pf_delay_ns);
     if (shape < 0 && use_pairs(M, N, K, splits)) return launch_pair(W, M, X, g, ldw, ldx, stream);
     return launch_shape(shape < 0 ? pick_shape(M, N, K, splits) : shape, W, X, g, ldw, ldx, splits, stream);
+}
+
+// A product over groups of tokens that each meet another matrix (the experts of a routed feed-forward).  W
+// [groups * group_rows, K]: the groups' matrices stacked; X [tiles * tile_rows, K]: the tokens sorted by group, every
+// group's run padded to whole tiles of tile_rows rows (16, 32, 64, 128 or 256); tile_group [tiles] (device): the group
+// of each tile, -1 for a tile beyond the last, whose rows are neither read nor written.  out [tiles * tile_rows,
+// group_rows] of out_dtype, after `act` (0: none, 2: SiLU, 3: the square of ReLU).  The grid is laid out for all
+// `tiles`; which of them hold tokens is read on the device, so a captured step replays the launch.
+VCB_API int vcb_gemm_bf16_grouped(const void* W, const void* X, void* out, int out_dtype, int groups, int group_rows, int tiles,
+                                  int tile_rows, int K, long long ldw, long long ldx, long long ldc, const int* tile_group,
+                                  int act, int* status, cudaStream_t stream) {
+    if (tiles == 0) return 0;
+    VCB_CHECK_ARG(groups > 0 && group_rows > 0 && tiles > 0 && K > 0, "gemm_bf16_grouped: bad sizes");
+    VCB_CHECK_ARG(K % 8 == 0 && ldw % 8 == 0 && ldx % 8 == 0,
+                  "gemm_bf16_grouped: inner size %d and row strides %lld, %lld must be multiples of 8 (16-byte rows for TMA)", K, ldw, ldx);
+    VCB_CHECK_ARG(((uintptr_t)W % 16 == 0) && ((uintptr_t)X % 16 == 0), "gemm_bf16_grouped: operands must be 16-byte aligned");
+    VCB_CHECK_ARG(tile_group != nullptr && (act == 0 || act == 2 || act == 3), "gemm_bf16_grouped: no tile table, or an unknown activation");
+    const int total_kb = (K + BK - 1) / BK;
+    GemmArgs g{out, out_dtype, group_rows, tiles * tile_rows, K, ldc, 0, total_kb, 1, 0, status};
+    g.tile_group = tile_group;
+    g.group_rows = group_rows;
+    g.act = act;
+    const long long w_rows = (long long)groups * group_rows;
+    switch (tile_rows) {
+        case 16: return launch_maps<16, 8, 1, 2>(W, w_rows, X, g, ldw, ldx, 1, stream);
+        case 32: return launch_maps<32, 8, 1, 2>(W, w_rows, X, g, ldw, ldx, 1, stream);
+        case 64: return launch_maps<64, 8, 1, 2>(W, w_rows, X, g, ldw, ldx, 1, stream);
+        case 128: return launch_maps<128, 6, 1, 2>(W, w_rows, X, g, ldw, ldx, 1, stream);
+        case 256: return launch_maps<256, 4, 1, 2>(W, w_rows, X, g, ldw, ldx, 1, stream);
+    }
+    vcb_set_error("gemm_bf16_grouped: tiles of %d rows (16, 32, 64, 128 or 256)", tile_rows);
+    return -1;
 }
 
 // Fused feed-forward front half.  W [2I, K] holds gate_i in row 2i and up_i in row 2i+1; out[t][i] =

@@ -20,7 +20,7 @@
 
 namespace {
 
-constexpr int BM = 32;    // rows (pairs) per tile
+constexpr int BM = 32;    // rows (pairs) per tile of the plain product below
 constexpr int BN = 64;    // output features per block
 constexpr int BK = 16;
 
@@ -94,7 +94,7 @@ __global__ void moe_route_kernel(Rows logits, const int* __restrict__ q_start, c
 }
 
 // one block: counts, padded offsets, the tiles' experts, then every pair's place
-__global__ void moe_group_kernel(const int* __restrict__ sel_e, int A, int E, int tiles_cap, int* __restrict__ pos_of,
+__global__ void moe_group_kernel(const int* __restrict__ sel_e, int A, int E, int tiles_cap, int BM, int* __restrict__ pos_of,
                                  int* __restrict__ src_of, int* __restrict__ tile_expert) {
     extern __shared__ int sh[];    // cnt[E], off[E]
     pdl_trigger();
@@ -226,6 +226,24 @@ __global__ __launch_bounds__(256) void moe_gemm_kernel(GemmArgs a) {
     }
 }
 
+// a block a sorted row: the token's row times the pair's weight, rounded to the compute dtype (zeros in padding rows)
+template <typename T>
+__global__ void moe_gather_kernel(const T* __restrict__ x, long long ldx, const int* __restrict__ src_of,
+                                  const float* __restrict__ sel_w, int top, int K, T* __restrict__ out) {
+    pdl_trigger();
+    pdl_wait();
+    const int pos = blockIdx.x;
+    const int pair = src_of[pos];
+    T* dst = out + (size_t)pos * K;
+    if (pair < 0) {
+        for (int k = threadIdx.x; k < K; k += blockDim.x) dst[k] = from_f32<T>(0.f);
+        return;
+    }
+    const T* src = x + (size_t)(pair / top) * ldx;
+    const float w = sel_w != nullptr ? sel_w[pair] : 1.f;
+    for (int k = threadIdx.x; k < K; k += blockDim.x) dst[k] = from_f32<T>(to_f32(src[k]) * w);
+}
+
 // grid (ceil(W / 256), rows): out[t] = shared[t] + sum over the token's pairs, in the router's order
 __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ pos_of, const float* __restrict__ sel_w,
                                    int top, Rows shared, const int* __restrict__ q_start, const int* __restrict__ q_len,
@@ -266,14 +284,15 @@ VCB_API int vcb_moe_route(const float* logits, int S, long long s_stride, long l
     return 0;
 }
 
-// A = T * top pairs.  pos_of [A]: a pair's row in the sorted order (-1: none); src_of [tiles_cap * BM]: the pair in a row
+// A = T * top pairs, tiles of tile_rows rows.  pos_of [A]: a pair's row in the sorted order (-1: none); src_of [tiles_cap * tile_rows]: the pair in a row
 // (-1: padding); tile_expert [tiles_cap]: the expert of a tile (-1: beyond the last).
-VCB_API int vcb_moe_group(const int* sel_e, int A, int E, int tiles_cap, int* pos_of, int* src_of, int* tile_expert,
-                          cudaStream_t stream) {
+VCB_API int vcb_moe_group(const int* sel_e, int A, int E, int tiles_cap, int tile_rows, int* pos_of, int* src_of,
+                          int* tile_expert, cudaStream_t stream) {
     if (A == 0) return 0;
+    VCB_CHECK_ARG(tile_rows >= 1, "moe_group: tiles of %d rows", tile_rows);
     const size_t smem = (size_t)2 * E * sizeof(int);
     VCB_CHECK_ARG(smem <= 48 * 1024, "moe_group: %d experts are more than the kernel's shared memory holds", E);
-    launch_pdl(moe_group_kernel, dim3(1), dim3(1024), smem, stream, sel_e, A, E, tiles_cap, pos_of, src_of, tile_expert);
+    launch_pdl(moe_group_kernel, dim3(1), dim3(1024), smem, stream, sel_e, A, E, tiles_cap, tile_rows, pos_of, src_of, tile_expert);
     VCB_CHECK_LAUNCH("moe_group");
     return 0;
 }
@@ -297,6 +316,21 @@ VCB_API int vcb_moe_gemm(const void* x, long long ldx, const void* w, int dtype,
         else launch_pdl(moe_gemm_kernel<__nv_bfloat16, false>, grid, dim3(256), 0, stream, a);
     }
     VCB_CHECK_LAUNCH("moe_gemm");
+    return 0;
+}
+
+// The tokens' rows in sorted order for a product that cannot read them through the order itself: out[pos] = x[token of
+// the pair at pos] * sel_w[pair] (null: as it is), zeros where no pair sits.  x [T][ldx], out [rows][K], both `dtype`.
+VCB_API int vcb_moe_gather(const void* x, long long ldx, int dtype, const int* src_of, const float* sel_w, int top, int rows,
+                           int K, void* out, cudaStream_t stream) {
+    if (rows == 0) return 0;
+    const int threads = K >= 2048 ? 256 : 128;
+    if (dtype == VCB_F32)
+        launch_pdl(moe_gather_kernel<float>, dim3(rows), dim3(threads), 0, stream, (const float*)x, ldx, src_of, sel_w, top, K, (float*)out);
+    else
+        launch_pdl(moe_gather_kernel<__nv_bfloat16>, dim3(rows), dim3(threads), 0, stream, (const __nv_bfloat16*)x, ldx, src_of, sel_w, top, K,
+                   (__nv_bfloat16*)out);
+    VCB_CHECK_LAUNCH("moe_gather");
     return 0;
 }
 

@@ -80,7 +80,9 @@ def _declare(L):
         "vcb_ssm_scan": [P, I, LL, LL, I, P, I, LL, P, P, P, P, LL, P, P, P, I, I, I, I, I, I, I, I, P, P, P, P],
         "vcb_gated_group_norm": [P, P, I, LL, LL, P, F, P, P, I, I, I, I, P, I, P],
         "vcb_moe_route": [P, I, LL, LL, P, P, I, I, I, I, I, P, P, P],
-        "vcb_moe_group": [P, I, I, I, P, P, P, P],
+        "vcb_moe_group": [P, I, I, I, I, P, P, P, P],
+        "vcb_moe_gather": [P, LL, I, P, P, I, I, I, P, P],
+        "vcb_gemm_bf16_grouped": [P, P, P, I, I, I, I, I, I, LL, LL, LL, P, I, P, P],
         "vcb_moe_gemm": [P, LL, P, I, P, P, P, I, I, P, I, I, I, I, P],
         "vcb_moe_combine": [P, P, P, I, P, I, LL, LL, P, P, I, I, I, P, P],
         "vcb_conv_state_update": [P, I, LL, LL, P, P, LL, P, P, P, I, I, I, P],
@@ -674,9 +676,10 @@ def moe_tile_rows() -> int:
     return int(lib().vcb_moe_tile_rows())
 
 
-def moe_tiles_cap(n_pairs: int, n_experts: int) -> int:
-    """The most tiles ``n_pairs`` pairs can fill when each of ``n_experts`` experts pads its own to whole tiles."""
-    return min(n_pairs, n_experts) + n_pairs // moe_tile_rows()
+def moe_tiles_cap(n_pairs: int, n_experts: int, tile_rows: int | None = None) -> int:
+    """The most tiles of ``tile_rows`` rows (default: the plain product's) that ``n_pairs`` pairs can fill when each of
+    ``n_experts`` experts pads its own to whole tiles."""
+    return min(n_pairs, n_experts) + n_pairs // (tile_rows or moe_tile_rows())
 
 
 def moe_route(logits, q_start, q_len, n_entries, top, sel_e, sel_w, softmax_weights=False):
@@ -691,13 +694,47 @@ def moe_route(logits, q_start, q_len, n_entries, top, sel_e, sel_w, softmax_weig
           _p(sel_e), _p(sel_w), _stream())
 
 
-def moe_group(sel_e, n_experts, tiles_cap, pos_of, src_of, tile_expert):
-    """Sorts the pairs by expert into tiles (see csrc/kernels/moe.cu)."""
+def moe_group(sel_e, n_experts, tiles_cap, pos_of, src_of, tile_expert, tile_rows=None):
+    """Sorts the pairs by expert into tiles of ``tile_rows`` rows (default: the plain product's; see csrc/kernels/moe.cu)."""
     for name, t in (("sel_e", sel_e), ("pos_of", pos_of), ("src_of", src_of), ("tile_expert", tile_expert)):
         _need(t, name, torch.int32)
     A = sel_e.numel()
-    assert pos_of.numel() == A and src_of.numel() == tiles_cap * moe_tile_rows() and tile_expert.numel() == tiles_cap
-    _call("vcb_moe_group", _p(sel_e), A, int(n_experts), int(tiles_cap), _p(pos_of), _p(src_of), _p(tile_expert), _stream())
+    tile_rows = int(tile_rows or moe_tile_rows())
+    assert pos_of.numel() == A and src_of.numel() == tiles_cap * tile_rows and tile_expert.numel() == tiles_cap
+    _call("vcb_moe_group", _p(sel_e), A, int(n_experts), int(tiles_cap), tile_rows, _p(pos_of), _p(src_of), _p(tile_expert),
+          _stream())
+
+
+GROUPED_TILE_ROWS = (16, 32, 64, 128, 256)     # token tiles of the grouped tensor-core product
+
+
+def moe_gather(x, src_of, sel_w, top, out):
+    """out[pos] = x[token of the pair at sorted row pos] * sel_w[pair] (None: as it is), zeros where no pair sits."""
+    _need(x, "x", contiguous=False); _need(out, "out", x.dtype); _need(src_of, "src_of", torch.int32)
+    rows, K = out.shape
+    assert x.shape[1] == K and x.stride(1) == 1 and src_of.numel() == rows
+    _call("vcb_moe_gather", _p(x), x.stride(0), _dt(x), _p(src_of), _p(sel_w), int(top), rows, K, _p(out), _stream())
+
+
+def gemm_grouped_ok(x, w) -> bool:
+    """Whether the grouped tensor-core product can address these operands (bfloat16, 16-byte rows and bases)."""
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and w.is_contiguous())
+
+
+def gemm_bf16_grouped(w, x, tile_expert, tile_rows, out, status, act=None):
+    """out[r, :] = act(w[tile_expert[r // tile_rows]] . x[r]) over the sorted rows (tcgen05 + TMA): w [E, N, K] bfloat16,
+    x [tiles * tile_rows, K] bfloat16, out [tiles * tile_rows, N] bfloat16 or float32; tiles whose expert is -1 are
+    skipped.  ``act``: None, "silu" or "relu2"."""
+    _need(w, "w", torch.bfloat16); _need(x, "x", torch.bfloat16, contiguous=False); _need(out, "out")
+    _need(tile_expert, "tile_expert", torch.int32)
+    E, N, K = w.shape
+    tiles = tile_expert.numel()
+    assert tile_rows in GROUPED_TILE_ROWS and x.shape == (tiles * tile_rows, K) and out.shape == (tiles * tile_rows, N)
+    if act not in (None, "silu", "relu2"):
+        raise KernelError(f"gemm_bf16_grouped: activation '{act}' (None, 'silu' or 'relu2')")
+    _call("vcb_gemm_bf16_grouped", _p(w), _p(x), _p(out), _dt(out), E, N, tiles, int(tile_rows), K, K, x.stride(0), out.stride(0),
+          _p(tile_expert), 0 if act is None else ACTIVATIONS[act], _p(status), _stream())
 
 
 def moe_gemm(x, w, tile_expert, out, *, src_of=None, sel_w=None, top=1, act=None):

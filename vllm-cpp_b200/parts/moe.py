@@ -21,6 +21,13 @@ from .base import FeedForward
 from .linear import matmul_tn
 
 
+def grouped_tile_rows(n_pairs: int, n_experts: int) -> int:
+    """Rows of a token tile of the grouped product: small tiles while an expert gets few of the step's pairs (a tile is
+    padded to its size), the products' widest once the experts' runs are long."""
+    avg = n_pairs / max(n_experts, 1)
+    return 16 if avg <= 8 else (32 if avg <= 24 else (64 if avg <= 48 else 128))
+
+
 class RoutedExperts(FeedForward):
     """params: ``hidden_size``, ``num_experts``, ``top``, ``expert_size`` (an expert's hidden size), ``shared_size`` (0:
     no shared expert), ``activation`` (default "relu2"), ``router_weights`` ("sigmoid" or "softmax"), ``weight_on``
@@ -69,17 +76,28 @@ class RoutedExperts(FeedForward):
         sel_w = workspace.empty((T, top), torch.float32, dev)
         ops.moe_route(side[..., sff:], ctx.q_start, ctx.q_len, ctx.E, top, sel_e, sel_w,
                       softmax_weights=self.router_weights == "softmax")
-        tiles = ops.moe_tiles_cap(T * top, E)
-        rows = tiles * ops.moe_tile_rows()
+        on_input = self.weight_on == "input"
+        # bfloat16 with rows the TMA unit can address: the experts' products on the tensor cores, the tokens' rows
+        # gathered (and weighted) in sorted order first; else the plain products, which read through the order
+        tensor_cores = (self.activation in ("relu2", "silu") and self.ff % 8 == 0 and ops.gemm_grouped_ok(x, self.w_up)
+                        and ops.gemm_grouped_ok(x, self.w_down))
+        tile_rows = grouped_tile_rows(T * top, E) if tensor_cores else ops.moe_tile_rows()
+        tiles = ops.moe_tiles_cap(T * top, E, tile_rows)
+        rows = tiles * tile_rows
         pos_of = workspace.empty((T * top,), torch.int32, dev)
         src_of = workspace.empty((rows,), torch.int32, dev)
         tile_expert = workspace.empty((tiles,), torch.int32, dev)
-        ops.moe_group(sel_e, E, tiles, pos_of, src_of, tile_expert)
-        on_input = self.weight_on == "input"
+        ops.moe_group(sel_e, E, tiles, pos_of, src_of, tile_expert, tile_rows)
         h1 = workspace.empty((rows, self.ff), x.dtype, dev)
-        ops.moe_gemm(x, self.w_up, tile_expert, h1, src_of=src_of, sel_w=sel_w if on_input else None, top=top, act=self.activation)
         y = workspace.empty((rows, H), torch.float32, dev)
-        ops.moe_gemm(h1, self.w_down, tile_expert, y)
+        if tensor_cores:
+            xs = workspace.empty((rows, H), x.dtype, dev)
+            ops.moe_gather(x, src_of, sel_w if on_input else None, top, xs)
+            ops.gemm_bf16_grouped(self.w_up, xs, tile_expert, tile_rows, h1, ctx.status, act=self.activation)
+            ops.gemm_bf16_grouped(self.w_down, h1, tile_expert, tile_rows, y, ctx.status)
+        else:
+            ops.moe_gemm(x, self.w_up, tile_expert, h1, src_of=src_of, sel_w=sel_w if on_input else None, top=top, act=self.activation)
+            ops.moe_gemm(h1, self.w_down, tile_expert, y)
         shared = None
         if sff:
             sa = workspace.empty((T, sff), x.dtype, dev)
