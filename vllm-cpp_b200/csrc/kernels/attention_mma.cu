@@ -84,6 +84,12 @@ struct AttnArgs {
     int keep_first;
     const float* dist_a;
     const float* dist_b;
+    // softcap c > 0: the scaled score becomes c tanh(s / c); slope [nh] (or null): slope_h (pos - j) is taken off it after
+    // the cap; sink: a silent key of score 0 without a value in every softmax (it enters as the starting state -- maximum
+    // 0, sum 1 -- of the first key slice's first key group, so slices and groups merge as they are)
+    float softcap;
+    const float* slope;
+    int sink;
 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
@@ -511,8 +517,9 @@ __global__ __launch_bounds__(WR * WK * 32 + (TMA ? 32 : 0)) void attn_mma_kernel
     for (int mr = 0; mr < MR; ++mr) {
 #pragma unroll
         for (int i = 0; i < ND; ++i) o[mr][i][0] = o[mr][i][1] = o[mr][i][2] = o[mr][i][3] = 0.f;
-        m_run[mr][0] = m_run[mr][1] = -CUDART_INF_F;
-        l_run[mr][0] = l_run[mr][1] = 0.f;   // per-thread partial sums (reduced over the quad at the end)
+        const bool with_sink = a.sink != 0 && slice == 0 && wk == 0;
+        m_run[mr][0] = m_run[mr][1] = with_sink ? 0.f : -CUDART_INF_F;
+        l_run[mr][0] = l_run[mr][1] = with_sink && (lane & 3) == 0 ? 1.f : 0.f;   // per-thread partial sums (reduced over the quad at the end)
         r_a[mr] = (wr * MR + mr) * 16 + (lane >> 2);
         pos_a[mr] = pos0 + r_a[mr] / gq;
         pos_b[mr] = pos0 + (r_a[mr] + 8) / gq;
@@ -528,7 +535,18 @@ __global__ __launch_bounds__(WR * WK * 32 + (TMA ? 32 : 0)) void attn_mma_kernel
         db_a[mr] = on && ok_a[mr] ? a.dist_b[ha] : 0.f;
         da_b[mr] = on && ok_b[mr] ? a.dist_a[hb] * 0.6931471805599453f : 0.f;
         db_b[mr] = on && ok_b[mr] ? a.dist_b[hb] : 0.f;
+        if (a.slope != nullptr) {      // (never together with the logarithmic penalty: the slope rides in its place)
+            da_a[mr] = ok_a[mr] ? a.slope[ha] : 0.f;
+            da_b[mr] = ok_b[mr] ? a.slope[hb] : 0.f;
+        }
     }
+    const bool lin = a.slope != nullptr || a.softcap > 0.f;
+    const float cap = a.softcap, cap_in = cap > 0.f ? 2.f / cap : 0.f;
+    // c tanh(v / c) = c (1 - 2 / (exp(2 v / c) + 1)), then the slope times the distance
+    auto lin_adj = [&](float v, float slope, float dist) {
+        if (cap > 0.f) v = fmaf(-2.f * cap, __fdividef(1.f, __expf(v * cap_in) + 1.f), cap);
+        return fmaf(-slope, dist, v);
+    };
 
     if (warp < NW) {
         // ---- one 16-row tile per warp: its Q fragments stay in registers; two: they are re-read per key tile ----
@@ -614,7 +632,19 @@ __global__ __launch_bounds__(WR * WK * 32 + (TMA ? 32 : 0)) void attn_mma_kernel
                 // k-th key: one multiply-add, one base-2 logarithm and one multiply-add a score (the fast logarithm's
                 // error, some 1e-6, is far below the rounding of the bfloat16 operands)
                 const float one_a = fmaf(db_a[mr], (float)(pos_a[mr] - kq), 1.f), one_b = fmaf(db_b[mr], (float)(pos_b[mr] - kq), 1.f);
-                if (all_inner && !penal) {
+                if (all_inner && lin) {
+#pragma unroll
+                    for (int i = 0; i < NS; ++i) {
+#pragma unroll
+                        for (int c = 0; c < 2; ++c) {
+                            const int kidx = kq + i * 8 + c;
+                            s[mr][i][c] = lin_adj(s[mr][i][c] * a.scale, da_a[mr], (float)(pos_a[mr] - kidx));
+                            s[mr][i][2 + c] = lin_adj(s[mr][i][2 + c] * a.scale, da_b[mr], (float)(pos_b[mr] - kidx));
+                            mx_a = fmaxf(mx_a, s[mr][i][c]);
+                            mx_b = fmaxf(mx_b, s[mr][i][2 + c]);
+                        }
+                    }
+                } else if (all_inner && !penal) {
 #pragma unroll
                     for (int i = 0; i < NS; ++i) {
 #pragma unroll
@@ -651,6 +681,9 @@ __global__ __launch_bounds__(WR * WK * 32 + (TMA ? 32 : 0)) void attn_mma_kernel
                                 const float k = (float)(i * 8 + c);
                                 if (sa) va = fmaf(-da_a[mr], __log2f(fmaf(-db_a[mr], k, one_a)), va);
                                 if (sb) vb = fmaf(-da_b[mr], __log2f(fmaf(-db_b[mr], k, one_b)), vb);
+                            } else if (lin) {
+                                if (sa) va = lin_adj(va, da_a[mr], (float)(pos_a[mr] - kidx));
+                                if (sb) vb = lin_adj(vb, da_b[mr], (float)(pos_b[mr] - kidx));
                             }
                             s[mr][i][c] = sa ? va : -CUDART_INF_F;
                             s[mr][i][2 + c] = sb ? vb : -CUDART_INF_F;
@@ -1066,7 +1099,7 @@ VCB_API int vcb_attn_mma_ex(const void* q, void* out, const void* pages, long lo
                             const int* ctx_len, const int* items, int n_items, int rows_max, float* part_o,
                             float* part_ml, int* slice_counters, const int* dec_rows, int nh, int nkv, int hd,
                             int page_size, int num_pages, int window, float scale, int keep_first, const float* dist_a,
-                            const float* dist_b, int* status, int allow_tma, int cluster, cudaStream_t stream);
+                            const float* dist_b, float softcap, const float* slope, int sink, int* status, int allow_tma, int cluster, cudaStream_t stream);
 
 VCB_API int vcb_attn_mma(const void* q, void* out, const void* pages, long long page_stride, const int* block_table,
                          const int* table_row, int max_blocks, const int* q_start, const int* q_len,
@@ -1076,16 +1109,16 @@ VCB_API int vcb_attn_mma(const void* q, void* out, const void* pages, long long 
                          int cluster, cudaStream_t stream) {
     return vcb_attn_mma_ex(q, out, pages, page_stride, block_table, table_row, max_blocks, q_start, q_len, ctx_len, items,
                            n_items, rows_max, part_o, part_ml, slice_counters, dec_rows, nh, nkv, hd, page_size, num_pages,
-                           window, scale, 0, nullptr, nullptr, status, allow_tma, cluster, stream);
+                           window, scale, 0, nullptr, nullptr, 0.f, nullptr, 0, status, allow_tma, cluster, stream);
 }
 
-// keep_first, dist_a, dist_b: the options described with AttnArgs.
+// keep_first, dist_a, dist_b, softcap, slope, sink: the options described with AttnArgs.
 VCB_API int vcb_attn_mma_ex(const void* q, void* out, const void* pages, long long page_stride, const int* block_table,
                             const int* table_row, int max_blocks, const int* q_start, const int* q_len,
                             const int* ctx_len, const int* items, int n_items, int rows_max, float* part_o,
                             float* part_ml, int* slice_counters, const int* dec_rows, int nh, int nkv, int hd,
                             int page_size, int num_pages, int window, float scale, int keep_first, const float* dist_a,
-                            const float* dist_b, int* status, int allow_tma, int cluster, cudaStream_t stream) {
+                            const float* dist_b, float softcap, const float* slope, int sink, int* status, int allow_tma, int cluster, cudaStream_t stream) {
     if (n_items == 0) return 0;
     VCB_CHECK_ARG(keep_first >= 0 && (dist_a == nullptr) == (dist_b == nullptr), "attn_mma: bad keep_first %d or half a distance penalty", keep_first);
     VCB_CHECK_ARG(nh > 0 && nkv > 0 && nh % nkv == 0, "attn_mma: %d query heads are not a multiple of %d KV heads", nh, nkv);
@@ -1094,7 +1127,8 @@ VCB_API int vcb_attn_mma_ex(const void* q, void* out, const void* pages, long lo
     VCB_CHECK_ARG(page_size > 0 && window >= 0, "attn_mma: bad page_size %d or window %d", page_size, window);
     AttnArgs a{(const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)pages, page_stride, block_table,
                table_row, max_blocks, q_start, q_len, ctx_len, items, part_o, part_ml, slice_counters, dec_rows, nh, nkv,
-               page_size, num_pages, window, scale, status, FusedQkv{}, cluster, keep_first, dist_a, dist_b};
+               page_size, num_pages, window, scale, status, FusedQkv{}, cluster, keep_first, dist_a, dist_b, softcap, slope, sink};
+    VCB_CHECK_ARG(softcap >= 0.f && (dist_a == nullptr || slope == nullptr), "attn_mma: a negative cap, or a logarithmic penalty and a slope at once");
     const bool tma = allow_tma && (page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64) &&
                      ((uintptr_t)pages % 16 == 0) && page_stride == (long long)2 * nkv * page_size * hd;
     if (hd == 64) return tma ? launch_rows<64, true>(a, n_items, rows_max, stream) : launch_rows<64, false>(a, n_items, rows_max, stream);

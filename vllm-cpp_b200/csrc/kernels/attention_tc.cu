@@ -75,6 +75,11 @@ struct TcArgs {
     int keep_first;
     const float* dist_a;
     const float* dist_b;
+    // softcap c > 0: the scaled score becomes c tanh(s / c); slope [nh] (or null): slope_h (pos - j) is taken off it
+    // after the cap; sink: a silent key of score 0 without a value joins every row's softmax
+    float softcap;
+    const float* slope;
+    int sink;
 };
 
 // a box of whole groups of 8 tokens, all lanes: coordinates (lane 0, token 0, half 0, group)
@@ -594,7 +599,12 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
             // the distance penalty of the row's head, in the base-2 domain the weights are computed in: a log2(1 + b d)
             const bool penal = OPT && a.dist_a != nullptr;
             const float pen_a = penal && row_ok ? a.dist_a[u.head0 + ih] : 0.f, pen_b = penal && row_ok ? a.dist_b[u.head0 + ih] : 0.f;
-            const float sl2 = penal ? 1.f : scale_log2;   // what is left to multiply the scores by on their way to weights
+            // a cap on the scaled score and a slope times the distance, likewise brought to the base-2 domain here
+            const bool lin = OPT && (a.slope != nullptr || a.softcap > 0.f);
+            const bool sink = OPT && a.sink != 0;
+            const float slope_l2 = lin && a.slope != nullptr && row_ok ? a.slope[u.head0 + ih] * LOG2E : 0.f;
+            const float cap_l2 = a.softcap * LOG2E, cap_in = a.softcap > 0.f ? 2.f * scale_log2 / a.softcap : 0.f;
+            const float sl2 = penal || lin ? 1.f : scale_log2;   // what is left to multiply the scores by on their way to weights
 
             // The row's query -> shared memory (rows beyond R are zero).  The products of the unit before have all
             // been waited for (its last P . V, and with it everything issued earlier), so nothing reads the old rows.
@@ -635,6 +645,19 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
                     for (int c = 0; c < BNK; ++c)
                         sv[c / 16][c % 16] = __float_as_uint(fmaf(-pen_a, __log2f(fmaf(-pen_b, (float)c, one)), __uint_as_float(sv[c / 16][c % 16]) * scale_log2));
                 }
+                if (lin) {
+                    // c tanh(s / c) = c (1 - 2 / (exp(2 s / c) + 1)): one exponential and one division a score; then
+                    // the slope times the distance (keys beyond the row's own position are masked below)
+                    const float d0 = (float)(pos_r - k0);
+#pragma unroll
+                    for (int c = 0; c < BNK; ++c) {
+                        const float raw = __uint_as_float(sv[c / 16][c % 16]);
+                        float x;
+                        if (a.softcap > 0.f) x = fmaf(-2.f * cap_l2, __fdividef(1.f, ex2_fast(raw * cap_in) + 1.f), cap_l2);
+                        else x = raw * scale_log2;
+                        sv[c / 16][c % 16] = __float_as_uint(fmaf(slope_l2, (float)c - d0, x));
+                    }
+                }
                 if (!plain_tile) {
                     const int kbeg = OPT && j < u.n_ft ? 0 : u.lo;
 #pragma unroll
@@ -648,7 +671,8 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
                 for (int c = 0; c < BNK; c += 2)
                     mx4[(c >> 1) & 3] = max3(mx4[(c >> 1) & 3], __uint_as_float(sv[c / 16][c % 16]), __uint_as_float(sv[c / 16][c % 16 + 1]));
                 // the scale is positive: the maximum of the scaled scores is the scaled maximum
-                const float m_new = fmaxf(fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sl2, m_ref);
+                float m_new = fmaxf(fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sl2, m_ref);
+                if (sink && j == 0) m_new = fmaxf(m_new, 0.f);   // the silent key of score 0 joins the row's first tile
                 // Move the reference when the maximum has outgrown it.  O (in TMEM) holds the sum so far against the
                 // old reference: the warp rescales its 32 rows together, rows that keep theirs by a factor of one.
                 const bool first_keys = m_ref == -CUDART_INF_F && m_new != -CUDART_INF_F;   // nothing summed yet
@@ -674,6 +698,7 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
                     l_run *= alpha;
                 }
                 if (grow || first_keys) m_ref = m_new;
+                if (sink && j == 0) l_run = exp2f(-m_ref);       // its weight against the reference (no value to add)
                 const float m_sub = m_ref == -CUDART_INF_F ? 0.f : m_ref;   // no key yet: every weight is exp2(-inf) = 0
 
                 uint64_t sum4[4] = {0ull, 0ull, 0ull, 0ull};   // four pairs of partial sums, all +0
@@ -801,7 +826,7 @@ VCB_API int vcb_attn_tc_supported(int dtype, int hd, int page_size) {
 VCB_API int vcb_attn_tc_ex(const void* q, void* out, const void* pages, long long page_stride, const int* block_table,
                            const int* table_row, int max_blocks, const int* q_start, const int* q_len, const int* ctx_len,
                            const int* items, int n_items, int nh, int nkv, int hd, int page_size, int num_pages, int window,
-                           float scale, int keep_first, const float* dist_a, const float* dist_b, int* status, int* work,
+                           float scale, int keep_first, const float* dist_a, const float* dist_b, float softcap, const float* slope, int sink, int* status, int* work,
                            cudaStream_t stream);
 
 // Prompt portions only: every item has slice 0 of 1 and at most 128 rows (tokens x query heads per KV head).
@@ -812,13 +837,13 @@ VCB_API int vcb_attn_tc(const void* q, void* out, const void* pages, long long p
                         const int* items, int n_items, int nh, int nkv, int hd, int page_size, int num_pages, int window,
                         float scale, int* status, int* work, cudaStream_t stream) {
     return vcb_attn_tc_ex(q, out, pages, page_stride, block_table, table_row, max_blocks, q_start, q_len, ctx_len, items, n_items,
-                          nh, nkv, hd, page_size, num_pages, window, scale, 0, nullptr, nullptr, status, work, stream);
+                          nh, nkv, hd, page_size, num_pages, window, scale, 0, nullptr, nullptr, 0.f, nullptr, 0, status, work, stream);
 }
 
 VCB_API int vcb_attn_tc_ex(const void* q, void* out, const void* pages, long long page_stride, const int* block_table,
                            const int* table_row, int max_blocks, const int* q_start, const int* q_len, const int* ctx_len,
                            const int* items, int n_items, int nh, int nkv, int hd, int page_size, int num_pages, int window,
-                           float scale, int keep_first, const float* dist_a, const float* dist_b, int* status, int* work,
+                           float scale, int keep_first, const float* dist_a, const float* dist_b, float softcap, const float* slope, int sink, int* status, int* work,
                            cudaStream_t stream) {
     if (n_items == 0) return 0;
     VCB_CHECK_ARG(keep_first >= 0 && (dist_a == nullptr) == (dist_b == nullptr), "attn_tc: bad keep_first %d or half a distance penalty", keep_first);
@@ -835,7 +860,8 @@ VCB_API int vcb_attn_tc_ex(const void* q, void* out, const void* pages, long lon
     const int g = nh / nkv;
     const int hchunks = (g + ROWS - 1) / ROWS;
     TcArgs a{(const __nv_bfloat16*)q, (__nv_bfloat16*)out, block_table, table_row, max_blocks, q_start, q_len, ctx_len,
-             items, nh, nkv, page_size, num_pages, window, scale, status, n_items * nkv * hchunks, work, keep_first, dist_a, dist_b};
-    if (keep_first > 0 || dist_a != nullptr) return hd == 64 ? launch<64, true>(map, a, n_items, stream) : launch<128, true>(map, a, n_items, stream);
+             items, nh, nkv, page_size, num_pages, window, scale, status, n_items * nkv * hchunks, work, keep_first, dist_a, dist_b, softcap, slope, sink};
+    VCB_CHECK_ARG(softcap >= 0.f && (dist_a == nullptr || slope == nullptr), "attn_tc: a negative cap, or a logarithmic penalty and a slope at once");
+    if (keep_first > 0 || dist_a != nullptr || softcap > 0.f || slope != nullptr || sink) return hd == 64 ? launch<64, true>(map, a, n_items, stream) : launch<128, true>(map, a, n_items, stream);
     return hd == 64 ? launch<64, false>(map, a, n_items, stream) : launch<128, false>(map, a, n_items, stream);
 }

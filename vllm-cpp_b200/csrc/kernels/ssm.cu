@@ -93,10 +93,13 @@ __device__ __forceinline__ bool find_chunk(const SsmArgs& a, int blk, int& e, in
 
 __device__ __forceinline__ float softplus_f(float z) { return fmaxf(z, 0.f) + log1pf(expf(-fabsf(z))); }
 
-// MODE 0: the local end state of a chunk from zero (no output); MODE 1: the outputs from the chunk's true start
+// MODE 0: the local end state of a chunk from zero (no output); MODE 1: the outputs from the chunk's true start.
+// A thread's state lanes: four runs of four neighbours, n = 4 (l + L c) + k for c, k < 4, so that the L threads of a
+// value lane read B and C as neighbouring 16-byte pieces (one conflict-free shared-memory load for all of them) and
+// the state itself in 16-byte pieces too.  Rows of B and C are padded with zeros to a multiple of four lanes.
 template <typename TX, int MODE>
 __global__ void ssm_scan_kernel(SsmArgs a) {
-    extern __shared__ float sm[];
+    extern __shared__ float4 sm4[];
     pdl_trigger();
     pdl_wait();
     int e, c, n, base;
@@ -104,43 +107,58 @@ __global__ void ssm_scan_kernel(SsmArgs a) {
     if (MODE == 0 && (n <= 1 || c == n - 1)) return;
     const int h = blockIdx.y, g = h / (a.heads / a.groups);
     const int N = a.N, P = a.P, PT = a.PT, L = a.L;
-    float* Bs = sm;                 // [NB][N]
-    float* Cs = Bs + NB * N;        // [NB][N]
-    float* xs = Cs + NB * N;        // [NB][PT]
-    float* dts = xs + NB * PT;      // [NB]
-    float* dAs = dts + NB;          // [NB]
+    const int N4 = (N + 3) >> 2;             // 16-byte pieces of a row of B or C
+    float4* Bs = sm4;                        // [NB][N4]
+    float4* Cs = Bs + NB * N4;               // [NB][N4]
+    float* xs = reinterpret_cast<float*>(Cs + NB * N4);   // [NB][PT]
+    float* dts = xs + NB * PT;               // [NB]
+    float* dAs = dts + NB;                   // [NB]
     const int tid = threadIdx.x;
     const int pl = tid / L, l = tid % L;
     const int p = blockIdx.z * PT + pl;
     const bool active = pl < PT && p < P;
-    const int n0 = l * a.npt;
-    const int cnt = active ? max(0, min(a.npt, N - n0)) : 0;
     const int inner = a.heads * P;
     const long long row0 = a.q_start[e] + (long long)c * a.Q;
     const int len = min(a.Q, a.q_len[e] - c * a.Q);
     const long long slot = a.slots[e];
-    const size_t hpn = ((size_t)h * P + (active ? p : 0)) * N + n0;
+    const size_t hp = ((size_t)h * P + (active ? p : 0)) * N;
+    const bool vec = (N & 3) == 0;
+    bool has[NPT / 4];
+#pragma unroll
+    for (int q = 0; q < NPT / 4; ++q) has[q] = active && l + L * q < N4;
 
     float S[NPT];
 #pragma unroll
     for (int i = 0; i < NPT; ++i) S[i] = 0.f;
     if (MODE == 1) {
-        const float* src = n > 1 ? a.scratch + (size_t)(base + c) * a.heads * P * N : a.state + slot * a.slot_stride;
+        const float* src = (n > 1 ? a.scratch + (size_t)(base + c) * a.heads * P * N : a.state + slot * a.slot_stride) + hp;
 #pragma unroll
-        for (int i = 0; i < NPT; ++i)
-            if (i < cnt) S[i] = src[hpn + i];
+        for (int q = 0; q < NPT / 4; ++q) {
+            if (!has[q]) continue;
+            const int n0 = 4 * (l + L * q);
+            if (vec) {
+                const float4 v = *reinterpret_cast<const float4*>(src + n0);
+                S[4 * q] = v.x; S[4 * q + 1] = v.y; S[4 * q + 2] = v.z; S[4 * q + 3] = v.w;
+            } else {
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    if (n0 + k < N) S[4 * q + k] = src[n0 + k];
+            }
+        }
     }
     const float rate = a.a[h], bias = a.dt_bias[h], Dh = a.D[h];
     const TX* xbc = reinterpret_cast<const TX*>(a.xbc);
+    float* Bf = reinterpret_cast<float*>(Bs);
+    float* Cf = reinterpret_cast<float*>(Cs);
     float decay = 1.f;
     for (int j0 = 0; j0 < len; j0 += NB) {
         const int nb = min(NB, len - j0);
         __syncthreads();
-        for (int i = tid; i < nb * N; i += blockDim.x) {
-            const int j = i / N, k = i % N;
+        for (int i = tid; i < nb * 4 * N4; i += blockDim.x) {
+            const int j = i / (4 * N4), k = i % (4 * N4);
             const TX* row = xbc + (row0 + j0 + j) * a.ldx;
-            Bs[j * N + k] = to_f32(row[inner + g * N + k]);
-            Cs[j * N + k] = to_f32(row[inner + (a.groups + g) * N + k]);
+            Bf[i] = k < N ? to_f32(row[inner + g * N + k]) : 0.f;
+            Cf[i] = k < N ? to_f32(row[inner + (a.groups + g) * N + k]) : 0.f;
         }
         for (int i = tid; i < nb * PT; i += blockDim.x) {
             const int j = i / PT, k = i % PT;
@@ -157,14 +175,24 @@ __global__ void ssm_scan_kernel(SsmArgs a) {
             const float dA = dAs[j];
             const float xv = active ? xs[j * PT + pl] : 0.f;
             const float dtx = dts[j] * xv;
-            const float* Bj = Bs + j * N + n0;
-            const float* Cj = Cs + j * N + n0;
+            const float4* Bj = Bs + j * N4 + l;
+            const float4* Cj = Cs + j * N4 + l;
             float acc = 0.f;
 #pragma unroll
-            for (int i = 0; i < NPT; ++i) {
-                if (i < cnt) {
-                    S[i] = fmaf(S[i], dA, dtx * Bj[i]);
-                    if (MODE == 1) acc = fmaf(S[i], Cj[i], acc);
+            for (int q = 0; q < NPT / 4; ++q) {
+                if (has[q]) {
+                    const float4 bv = Bj[L * q];
+                    S[4 * q] = fmaf(S[4 * q], dA, dtx * bv.x);
+                    S[4 * q + 1] = fmaf(S[4 * q + 1], dA, dtx * bv.y);
+                    S[4 * q + 2] = fmaf(S[4 * q + 2], dA, dtx * bv.z);
+                    S[4 * q + 3] = fmaf(S[4 * q + 3], dA, dtx * bv.w);
+                    if (MODE == 1) {
+                        const float4 cv = Cj[L * q];
+                        acc = fmaf(S[4 * q], cv.x, acc);
+                        acc = fmaf(S[4 * q + 1], cv.y, acc);
+                        acc = fmaf(S[4 * q + 2], cv.z, acc);
+                        acc = fmaf(S[4 * q + 3], cv.w, acc);
+                    }
                 }
             }
             if (MODE == 1) {
@@ -175,21 +203,31 @@ __global__ void ssm_scan_kernel(SsmArgs a) {
             }
         }
     }
+    float* dst = nullptr;
     if (MODE == 0) {
-        float* dst = a.scratch + (size_t)(base + c) * a.heads * P * N;
-#pragma unroll
-        for (int i = 0; i < NPT; ++i)
-            if (i < cnt) dst[hpn + i] = S[i];
+        dst = a.scratch + (size_t)(base + c) * a.heads * P * N + hp;
         if (tid == 0 && blockIdx.z == 0) a.chunk_decay[(size_t)(base + c) * a.heads + h] = decay;
     } else if (c == n - 1) {
-        float* dst = a.state + slot * a.slot_stride;
+        dst = a.state + slot * a.slot_stride + hp;
+    }
+    if (dst != nullptr) {
 #pragma unroll
-        for (int i = 0; i < NPT; ++i)
-            if (i < cnt) dst[hpn + i] = S[i];
+        for (int q = 0; q < NPT / 4; ++q) {
+            if (!has[q]) continue;
+            const int n0 = 4 * (l + L * q);
+            if (vec) {
+                *reinterpret_cast<float4*>(dst + n0) = make_float4(S[4 * q], S[4 * q + 1], S[4 * q + 2], S[4 * q + 3]);
+            } else {
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    if (n0 + k < N) dst[n0 + k] = S[4 * q + k];
+            }
+        }
     }
 }
 
-// grid (entries, heads); the threads walk the head's P x N state elements
+// grid (entries, heads, slices of the head's P x N state elements): a thread an element, chunk after chunk; the next
+// chunk's local state is asked for before this chunk's start is stored
 __global__ void ssm_chunk_carry_kernel(SsmArgs a) {
     pdl_trigger();
     pdl_wait();
@@ -199,15 +237,18 @@ __global__ void ssm_chunk_carry_kernel(SsmArgs a) {
     int base = 0;
     for (int i = 0; i < e; ++i) base += (a.q_len[i] + a.Q - 1) / a.Q;
     const size_t per_head = (size_t)a.P * a.N, per_chunk = per_head * a.heads;
-    const float* st = a.state + (long long)a.slots[e] * a.slot_stride + h * per_head;
-    for (size_t i = threadIdx.x; i < per_head; i += blockDim.x) {
-        float S = st[i];
-        for (int c = 0; c < n; ++c) {
-            float* at = a.scratch + (size_t)(base + c) * per_chunk + h * per_head + i;
-            const float local = c < n - 1 ? *at : 0.f;
-            *at = S;
-            if (c < n - 1) S = fmaf(a.chunk_decay[(size_t)(base + c) * a.heads + h], S, local);
-        }
+    const size_t i = (size_t)blockIdx.z * blockDim.x + threadIdx.x;
+    if (i >= per_head) return;
+    float S = a.state[(long long)a.slots[e] * a.slot_stride + h * per_head + i];
+    float* at = a.scratch + (size_t)base * per_chunk + h * per_head + i;
+    const float* dec = a.chunk_decay + (size_t)base * a.heads + h;
+    float local = *at;
+    for (int c = 0; c < n; ++c) {
+        const float next = c + 1 < n - 1 ? at[per_chunk] : 0.f;
+        *at = S;
+        if (c < n - 1) S = fmaf(dec[(size_t)c * a.heads], S, local);
+        local = next;
+        at += per_chunk;
     }
 }
 
@@ -252,8 +293,8 @@ VCB_API int vcb_ssm_scan(const float* u, int S, long long s_stride, long long ld
     VCB_CHECK_ARG(!multi || (scratch != nullptr && chunk_decay != nullptr), "ssm_scan: chunks need their scratch");
     VCB_CHECK_ARG(n_chunks <= 0x7fffffff / 1 && heads <= 65535 && E <= 65535, "ssm_scan: too many heads or entries");
     int L = 1;
-    while (L * NPT < N) L <<= 1;
-    const int npt = (N + L - 1) / L;
+    while (L * NPT < 4 * ((N + 3) / 4)) L <<= 1;
+    const int npt = NPT;
     int PT = 256 / L;
     if (PT < 1) PT = 1;
     if (PT > P) PT = P;
@@ -262,14 +303,14 @@ VCB_API int vcb_ssm_scan(const float* u, int S, long long s_stride, long long ld
     VCB_CHECK_ARG(ptiles <= 65535, "ssm_scan: too many tiles of value lanes");
     SsmArgs args{Rows{u, S < 1 ? 1 : S, s_stride, ld}, dt_col, xbc, ldx, dt_bias, a_rate, D, state, slot_stride, q_start, q_len,
                  slots, E, heads, P, N, groups, Q, scratch, chunk_decay, y, L, npt, PT};
-    const size_t smem = ((size_t)2 * NB * N + (size_t)NB * PT + 2 * NB) * sizeof(float);
+    const size_t smem = ((size_t)2 * NB * 4 * ((N + 3) / 4) + (size_t)NB * PT + 2 * NB) * sizeof(float);
     const dim3 grid(n_chunks, heads, ptiles);
     const bool f32 = xbc_dtype == VCB_F32;
     if (multi) {
         if (f32) launch_pdl(ssm_scan_kernel<float, 0>, grid, dim3(threads), smem, stream, args);
         else launch_pdl(ssm_scan_kernel<__nv_bfloat16, 0>, grid, dim3(threads), smem, stream, args);
         VCB_CHECK_LAUNCH("ssm_chunk_state");
-        launch_pdl(ssm_chunk_carry_kernel, dim3(E, heads), dim3(256), 0, stream, args);
+        launch_pdl(ssm_chunk_carry_kernel, dim3(E, heads, (unsigned)(((size_t)P * N + 255) / 256)), dim3(256), 0, stream, args);
         VCB_CHECK_LAUNCH("ssm_chunk_carry");
     }
     if (f32) launch_pdl(ssm_scan_kernel<float, 1>, grid, dim3(threads), smem, stream, args);

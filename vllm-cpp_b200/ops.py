@@ -93,14 +93,14 @@ def _declare(L):
         "vcb_selftest_wait_timeout": [LL, P, P, P],
         "vcb_state_reset": [P, I, LL, LL, LL, I, I, P, P, P, I, ctypes.c_uint, P, P],
         "vcb_attn_mma": [P, P, P, LL, P, P, I, P, P, P, P, I, I, P, P, P, P, I, I, I, I, I, I, F, P, I, I, P],
-        "vcb_attn_mma_ex": [P, P, P, LL, P, P, I, P, P, P, P, I, I, P, P, P, P, I, I, I, I, I, I, F, I, P, P, P, I, I, P],
+        "vcb_attn_mma_ex": [P, P, P, LL, P, P, I, P, P, P, P, I, I, P, P, P, P, I, I, I, I, I, I, F, I, P, P, F, P, I, P, I, I, P],
         "vcb_attn_mma_supported": [I, I],
         "vcb_attn_mma_max_clusters": [I, I, I],
         "vcb_attn_mma_fused_supported": [I, I, I],
         "vcb_attn_mma_decode_fused": [P, I, LL, P, P, I, I, F, P, I, P, P, P, LL, P, P, I, P, P, P, P, I, P, P, P, P, I, I,
                                       I, I, I, I, F, P, I, P],
         "vcb_attn_tc": [P, P, P, LL, P, P, I, P, P, P, P, I, I, I, I, I, I, I, F, P, P, P],
-        "vcb_attn_tc_ex": [P, P, P, LL, P, P, I, P, P, P, P, I, I, I, I, I, I, I, F, I, P, P, P, P, P],
+        "vcb_attn_tc_ex": [P, P, P, LL, P, P, I, P, P, P, P, I, I, I, I, I, I, I, F, I, P, P, F, P, I, P, P, P],
         "vcb_attn_tc_supported": [I, I, I],
         "vcb_attn_stream": [P, P, P, LL, P, P, I, P, P, P, I, P, I, I, I, I, I, I, F, P, I, P],
         "vcb_attn_stream_supported": [I, I, I, I, I],
@@ -885,9 +885,10 @@ def attn_tc_supported(dtype: torch.dtype, hd: int, page_size: int) -> bool:
 
 
 def attn_tc(q, out, pages, block_table, q_start, q_len, ctx_len, items, n_items, nh, nkv, hd, window, status,
-            table_row=None, work=None, scale=None, keep_first=0, dist_a=None, dist_b=None):
+            table_row=None, work=None, scale=None, keep_first=0, dist_a=None, dist_b=None, softcap=0.0, slope=None, sink=False):
     """Attention of prompt portions on tcgen05 tensor cores (bfloat16, head_dim 64 or 128, pages of 8 to 64
-    tokens), with the options of :func:`attn_window_bias` (``scale``, ``keep_first``, ``dist_a``/``dist_b``).
+    tokens), with the options of :func:`attn_window_bias` (``scale``, ``keep_first``, ``dist_a``/``dist_b``, ``softcap``,
+    ``slope``, ``sink``).
     Items as for :func:`attn_paged` with one key slice and at most 128 rows each.  ``work``: two int32
     zeros, zero again when the kernel is through (the queue its blocks take their units from); launches that share
     them must follow one another on a stream.  Made on the spot when not given."""
@@ -903,17 +904,20 @@ def attn_tc(q, out, pages, block_table, q_start, q_len, ctx_len, items, n_items,
     if dist_a is not None:
         _need(dist_a, "dist_a", torch.float32); _need(dist_b, "dist_b", torch.float32)
         assert dist_a.numel() == nh and dist_b.numel() == nh
+    if slope is not None:
+        _need(slope, "slope", torch.float32); assert slope.numel() == nh
     _call("vcb_attn_tc_ex", _p(q), _p(out), _p(pages), pages.stride(0), _p(block_table), _p(table_row),
           block_table.shape[1], _p(q_start), _p(q_len), _p(ctx_len), _p(items), n_items, nh, nkv, hd, page_size,
           num_pages, int(window or 0), 1.0 / math.sqrt(hd) if scale is None else float(scale), int(keep_first or 0),
-          _p(dist_a), _p(dist_b), _p(status), _p(work), _stream())
+          _p(dist_a), _p(dist_b), float(softcap or 0.0), _p(slope), int(bool(sink)), _p(status), _p(work), _stream())
 
 
 def attn_mma(q, out, pages, block_table, q_start, q_len, ctx_len, items, n_items, rows_max, part_o, part_ml,
              nh, nkv, hd, window, status, table_row=None, allow_tma=True, slice_counters=None, dec_rows=None,
-             cluster=0, scale=None, keep_first=0, dist_a=None, dist_b=None):
+             cluster=0, scale=None, keep_first=0, dist_a=None, dist_b=None, softcap=0.0, slope=None, sink=False):
     """Tensor-core variant of :func:`attn_paged` (bfloat16, head_dim 64 or 128; rows_max 16 or 128), with the
-    options of :func:`attn_window_bias` (``scale``, default 1/sqrt(hd); ``keep_first``; ``dist_a``/``dist_b``).
+    options of :func:`attn_window_bias` (``scale``, default 1/sqrt(hd); ``keep_first``; ``dist_a``/``dist_b``;
+    ``softcap``, ``slope``, ``sink``).
     With ``slice_counters`` (int32 zeros, one per decoded token and KV head group, left at zero again) and
     ``dec_rows``, the block that finishes a token's last key slice merges the slices itself; with ``cluster`` = the
     number of slices per token (2 to 8) as well, the slices' blocks run as a cluster and merge through shared memory."""
@@ -926,11 +930,13 @@ def attn_mma(q, out, pages, block_table, q_start, q_len, ctx_len, items, n_items
     if dist_a is not None:
         _need(dist_a, "dist_a", torch.float32); _need(dist_b, "dist_b", torch.float32)
         assert dist_a.numel() == nh and dist_b.numel() == nh
+    if slope is not None:
+        _need(slope, "slope", torch.float32); assert slope.numel() == nh
     _call("vcb_attn_mma_ex", _p(q), _p(out), _p(pages), pages.stride(0), _p(block_table), _p(table_row),
           block_table.shape[1], _p(q_start), _p(q_len), _p(ctx_len), _p(items), n_items, rows_max, _p(part_o),
           _p(part_ml), _p(slice_counters), _p(dec_rows), nh, nkv, hd, page_size, num_pages, int(window or 0),
-          1.0 / math.sqrt(hd) if scale is None else float(scale), int(keep_first or 0), _p(dist_a), _p(dist_b), _p(status),
-          int(allow_tma), int(cluster), _stream())
+          1.0 / math.sqrt(hd) if scale is None else float(scale), int(keep_first or 0), _p(dist_a), _p(dist_b),
+          float(softcap or 0.0), _p(slope), int(bool(sink)), _p(status), int(allow_tma), int(cluster), _stream())
 
 
 def attn_stream_supported(dtype: torch.dtype, hd: int, page_size: int, nh: int, nkv: int) -> bool:

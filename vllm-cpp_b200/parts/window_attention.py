@@ -42,7 +42,7 @@ from .linear import matmul_tn
 # 0 keeps every step on the plain attention kernel (comparison runs, tests)
 MMA_ATTENTION = os.environ.get("VLLM_CPP_B200_WINDOW_ATTN_MMA", "1") != "0"
 # whether the tensor-core kernels take the cap, the slope and the sink (else steps with them run on the plain kernel)
-EXTRAS_ON_TENSOR_CORES = False
+EXTRAS_ON_TENSOR_CORES = True
 
 
 class ConvWindowAttention(Mixer):
@@ -156,7 +156,7 @@ class ConvWindowAttention(Mixer):
         plan = ctx.plan(("attention", nh, nkv, mma, clustered, reach),
                         lambda: AttentionPlan(ctx, nh, nkv, dec_rows, span_rows, clustered, max_keys=reach))
         common = dict(nh=nh, nkv=nkv, hd=hd, window=self.window, status=ctx.status, table_row=ctx.slots, scale=self.scale,
-                      keep_first=self.keep_first, dist_a=self.dist_a, dist_b=self.dist_b)
+                      keep_first=self.keep_first, dist_a=self.dist_a, dist_b=self.dist_b, **extras)
         args = (q, out, kv.pages, group.block_table, ctx.q_start, ctx.q_len, ctx.ctx_len)
         if plan.n_dec:
             S = plan.nslices
@@ -170,7 +170,7 @@ class ConvWindowAttention(Mixer):
                              slice_counters=plan.slice_counters if S > 1 else None, dec_rows=plan.dec_rows, cluster=cluster,
                              **common)
             else:
-                ops.attn_window_bias(*args, plan.dec_items, plan.n_dec * S, dec_rows, part_o, part_ml, hd_v=vd, **common, **extras)
+                ops.attn_window_bias(*args, plan.dec_items, plan.n_dec * S, dec_rows, part_o, part_ml, hd_v=vd, **common)
                 if S > 1:
                     ops.attn_merge(part_o, part_ml, plan.dec_rows, out, plan.n_dec, nh, vd, S)
         if plan.n_span_items:
@@ -179,5 +179,5 @@ class ConvWindowAttention(Mixer):
             elif mma:
                 ops.attn_mma(*args, plan.span_items, plan.n_span_items, span_rows, None, None, **common)
             else:
-                ops.attn_window_bias(*args, plan.span_items, plan.n_span_items, span_rows, None, None, hd_v=vd, **common, **extras)
+                ops.attn_window_bias(*args, plan.span_items, plan.n_span_items, span_rows, None, None, hd_v=vd, **common)
         return matmul_tn(out, self.w_o, ctx.status, out_dtype=torch.float32, allow_partials=True)
