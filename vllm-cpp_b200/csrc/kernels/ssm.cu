@@ -27,7 +27,8 @@
 
 namespace {
 
-constexpr int NPT = 16;   // state lanes a thread holds at most
+constexpr int NPT = 16;   // state lanes of one value lane that a thread holds at most
+constexpr int PP = 4;     // value lanes a thread holds: what it reads of B and C from shared memory serves all of them
 constexpr int NB = 16;    // tokens staged at a time
 
 struct Rows {
@@ -74,7 +75,7 @@ struct SsmArgs {
     float* scratch;       // [chunks][heads][P][N]
     float* chunk_decay;   // [chunks][heads]
     float* y;             // [T][heads P]
-    int L, npt, PT;       // lanes per value lane (a power of two up to 32), state lanes per thread, value lanes per block
+    int L, npt, PT;       // threads per value lane (a power of two up to 32), 16-byte pieces of the state per thread, value lanes per block
 };
 
 // which entry and which of its chunks a chunk index is; false when there is no such chunk
@@ -93,12 +94,33 @@ __device__ __forceinline__ bool find_chunk(const SsmArgs& a, int blk, int& e, in
 
 __device__ __forceinline__ float softplus_f(float z) { return fmaxf(z, 0.f) + log1pf(expf(-fabsf(z))); }
 
+__device__ __forceinline__ uint64_t pair_f32(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpair_f32(uint64_t v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma_pair(uint64_t x, uint64_t y, uint64_t z) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(x), "l"(y), "l"(z));
+    return d;
+}
+__device__ __forceinline__ uint64_t mul_pair(uint64_t x, uint64_t y) {
+    uint64_t d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(x), "l"(y));
+    return d;
+}
+
 // MODE 0: the local end state of a chunk from zero (no output); MODE 1: the outputs from the chunk's true start.
-// A thread's state lanes: four runs of four neighbours, n = 4 (l + L c) + k for c, k < 4, so that the L threads of a
-// value lane read B and C as neighbouring 16-byte pieces (one conflict-free shared-memory load for all of them) and
-// the state itself in 16-byte pieces too.  Rows of B and C are padded with zeros to a multiple of four lanes.
-template <typename TX, int MODE>
-__global__ void ssm_scan_kernel(SsmArgs a) {
+// L: threads that share a value lane (a power of two).  A thread's state lanes: up to four runs of four neighbours,
+// n = 4 (l + L q) + k for q, k < 4, so that the L threads of a value lane read B and C as neighbouring 16-byte pieces
+// (one conflict-free shared-memory load for all of them) and the state itself in 16-byte pieces too; the arithmetic
+// runs on pairs of 32-bit lanes (fma.rn.f32x2: each lane an IEEE multiply-add).  Rows of B and C are padded with
+// zeros to nq * L pieces, so a thread beyond the last state lane keeps zeros without being asked.
+template <typename TX, int MODE, int L>
+__global__ __launch_bounds__(256) void ssm_scan_kernel(SsmArgs a) {
     extern __shared__ float4 sm4[];
     pdl_trigger();
     pdl_wait();
@@ -106,43 +128,53 @@ __global__ void ssm_scan_kernel(SsmArgs a) {
     if (!find_chunk(a, blockIdx.x, e, c, n, base)) return;
     if (MODE == 0 && (n <= 1 || c == n - 1)) return;
     const int h = blockIdx.y, g = h / (a.heads / a.groups);
-    const int N = a.N, P = a.P, PT = a.PT, L = a.L;
-    const int N4 = (N + 3) >> 2;             // 16-byte pieces of a row of B or C
+    const int N = a.N, P = a.P, PT = a.PT;
+    const int nq = a.npt;                    // 16-byte pieces a thread holds (1 to 4), the same for all
+    const int N4 = nq * L;                   // 16-byte pieces of a padded row of B or C
     float4* Bs = sm4;                        // [NB][N4]
     float4* Cs = Bs + NB * N4;               // [NB][N4]
-    float* xs = reinterpret_cast<float*>(Cs + NB * N4);   // [NB][PT]
-    float* dts = xs + NB * PT;               // [NB]
-    float* dAs = dts + NB;                   // [NB]
+    float* xs = reinterpret_cast<float*>(Cs + NB * N4);   // [NB][PT] x
+    float* dxs = xs + NB * PT;               // [NB][PT] dt * x
+    float* ys = dxs + NB * PT;               // [NB][PT] outputs of the staged tokens
+    float* dAs = ys + NB * PT;               // [NB]
     const int tid = threadIdx.x;
     const int pl = tid / L, l = tid % L;
-    const int p = blockIdx.z * PT + pl;
-    const bool active = pl < PT && p < P;
+    const int PG = PT / PP;                  // threads (of equal l) side by side: value lane k of thread pl is pl + k PG
+    const int p0 = blockIdx.z * PT;
+    const bool mine = pl < PG;
     const int inner = a.heads * P;
     const long long row0 = a.q_start[e] + (long long)c * a.Q;
     const int len = min(a.Q, a.q_len[e] - c * a.Q);
     const long long slot = a.slots[e];
-    const size_t hp = ((size_t)h * P + (active ? p : 0)) * N;
     const bool vec = (N & 3) == 0;
-    bool has[NPT / 4];
-#pragma unroll
-    for (int q = 0; q < NPT / 4; ++q) has[q] = active && l + L * q < N4;
+    const size_t head_at = (size_t)h * P * N;
 
-    float S[NPT];
+    uint64_t S2[PP][NPT / 2];
 #pragma unroll
-    for (int i = 0; i < NPT; ++i) S[i] = 0.f;
-    if (MODE == 1) {
-        const float* src = (n > 1 ? a.scratch + (size_t)(base + c) * a.heads * P * N : a.state + slot * a.slot_stride) + hp;
+    for (int k = 0; k < PP; ++k)
 #pragma unroll
-        for (int q = 0; q < NPT / 4; ++q) {
-            if (!has[q]) continue;
-            const int n0 = 4 * (l + L * q);
-            if (vec) {
-                const float4 v = *reinterpret_cast<const float4*>(src + n0);
-                S[4 * q] = v.x; S[4 * q + 1] = v.y; S[4 * q + 2] = v.z; S[4 * q + 3] = v.w;
-            } else {
+        for (int i = 0; i < NPT / 2; ++i) S2[k][i] = 0ull;
+    if (MODE == 1 && mine) {
+        const float* src = (n > 1 ? a.scratch + (size_t)(base + c) * a.heads * P * N : a.state + slot * a.slot_stride) + head_at;
 #pragma unroll
-                for (int k = 0; k < 4; ++k)
-                    if (n0 + k < N) S[4 * q + k] = src[n0 + k];
+        for (int k = 0; k < PP; ++k) {
+            const int p = p0 + pl + k * PG;
+            if (p >= P) continue;
+#pragma unroll
+            for (int q = 0; q < NPT / 4; ++q) {
+                const int n0 = 4 * (l + L * q);
+                if (q >= nq || n0 >= N) continue;
+                const float* at = src + (size_t)p * N + n0;
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (vec) v = *reinterpret_cast<const float4*>(at);
+                else {
+                    v.x = at[0];
+                    if (n0 + 1 < N) v.y = at[1];
+                    if (n0 + 2 < N) v.z = at[2];
+                    if (n0 + 3 < N) v.w = at[3];
+                }
+                S2[k][2 * q] = pair_f32(v.x, v.y);
+                S2[k][2 * q + 1] = pair_f32(v.z, v.w);
             }
         }
     }
@@ -150,77 +182,133 @@ __global__ void ssm_scan_kernel(SsmArgs a) {
     const TX* xbc = reinterpret_cast<const TX*>(a.xbc);
     float* Bf = reinterpret_cast<float*>(Bs);
     float* Cf = reinterpret_cast<float*>(Cs);
+    const int Np = 4 * N4;
+    // rows of B and C that can be fetched eight 16-bit values at a time
+    const bool vec8 = sizeof(TX) == 2 && (N & 7) == 0 && (a.ldx & 7) == 0 && ((inner + g * N) & 7) == 0 && (((a.groups) * N) & 7) == 0 &&
+                      ((uintptr_t)a.xbc & 15) == 0;
     float decay = 1.f;
     for (int j0 = 0; j0 < len; j0 += NB) {
         const int nb = min(NB, len - j0);
         __syncthreads();
-        for (int i = tid; i < nb * 4 * N4; i += blockDim.x) {
-            const int j = i / (4 * N4), k = i % (4 * N4);
-            const TX* row = xbc + (row0 + j0 + j) * a.ldx;
-            Bf[i] = k < N ? to_f32(row[inner + g * N + k]) : 0.f;
-            Cf[i] = k < N ? to_f32(row[inner + (a.groups + g) * N + k]) : 0.f;
+        if (vec8) {
+            const int per_row = Np >> 3;          // (N is a multiple of 8: no padding inside a piece of eight)
+            for (int i = tid; i < nb * per_row; i += blockDim.x) {
+                const int j = i / per_row, k = (i % per_row) * 8;
+                float4 b0 = make_float4(0.f, 0.f, 0.f, 0.f), b1 = b0, c0 = b0, c1 = b0;
+                if (k < N) {
+                    const __nv_bfloat16* row = reinterpret_cast<const __nv_bfloat16*>(xbc) + (row0 + j0 + j) * a.ldx + inner + g * N + k;
+                    const uint4 ub = *reinterpret_cast<const uint4*>(row);
+                    const uint4 uc = *reinterpret_cast<const uint4*>(row + (size_t)a.groups * N);
+                    b0 = make_float4(__uint_as_float(ub.x << 16), __uint_as_float(ub.x & 0xffff0000u), __uint_as_float(ub.y << 16), __uint_as_float(ub.y & 0xffff0000u));
+                    b1 = make_float4(__uint_as_float(ub.z << 16), __uint_as_float(ub.z & 0xffff0000u), __uint_as_float(ub.w << 16), __uint_as_float(ub.w & 0xffff0000u));
+                    c0 = make_float4(__uint_as_float(uc.x << 16), __uint_as_float(uc.x & 0xffff0000u), __uint_as_float(uc.y << 16), __uint_as_float(uc.y & 0xffff0000u));
+                    c1 = make_float4(__uint_as_float(uc.z << 16), __uint_as_float(uc.z & 0xffff0000u), __uint_as_float(uc.w << 16), __uint_as_float(uc.w & 0xffff0000u));
+                }
+                Bs[j * N4 + (k >> 2)] = b0; Bs[j * N4 + (k >> 2) + 1] = b1;
+                Cs[j * N4 + (k >> 2)] = c0; Cs[j * N4 + (k >> 2) + 1] = c1;
+            }
+        } else {
+            for (int i = tid; i < nb * Np; i += blockDim.x) {
+                const int j = i / Np, k = i % Np;
+                const TX* row = xbc + (row0 + j0 + j) * a.ldx;
+                Bf[i] = k < N ? to_f32(row[inner + g * N + k]) : 0.f;
+                Cf[i] = k < N ? to_f32(row[inner + (a.groups + g) * N + k]) : 0.f;
+            }
         }
+        if (tid < nb) dAs[tid] = softplus_f(rows_at(a.u, row0 + j0 + tid, a.dt_col + h) + bias);   // dt for now
+        __syncthreads();
         for (int i = tid; i < nb * PT; i += blockDim.x) {
             const int j = i / PT, k = i % PT;
-            const int pp = blockIdx.z * PT + k;
-            xs[j * PT + k] = pp < P ? to_f32(xbc[(row0 + j0 + j) * a.ldx + h * P + pp]) : 0.f;
+            const float x = p0 + k < P ? to_f32(xbc[(row0 + j0 + j) * a.ldx + h * P + p0 + k]) : 0.f;
+            xs[i] = x;
+            dxs[i] = dAs[j] * x;
         }
-        if (tid < nb) {
-            const float dt = softplus_f(rows_at(a.u, row0 + j0 + tid, a.dt_col + h) + bias);
-            dts[tid] = dt;
-            dAs[tid] = expf(-rate * dt);
-        }
+        __syncthreads();
+        if (tid < nb) dAs[tid] = expf(-rate * dAs[tid]);
         __syncthreads();
         for (int j = 0; j < nb; ++j) {
             const float dA = dAs[j];
-            const float xv = active ? xs[j * PT + pl] : 0.f;
-            const float dtx = dts[j] * xv;
+            const uint64_t dA2 = pair_f32(dA, dA);
+            uint64_t dtx2[PP], acc_lo[PP], acc_hi[PP];
+#pragma unroll
+            for (int k = 0; k < PP; ++k) {
+                const float dtx = mine ? dxs[j * PT + pl + k * PG] : 0.f;
+                dtx2[k] = pair_f32(dtx, dtx);
+                acc_lo[k] = acc_hi[k] = 0ull;
+            }
             const float4* Bj = Bs + j * N4 + l;
             const float4* Cj = Cs + j * N4 + l;
-            float acc = 0.f;
 #pragma unroll
             for (int q = 0; q < NPT / 4; ++q) {
-                if (has[q]) {
+                if (q < nq) {
                     const float4 bv = Bj[L * q];
-                    S[4 * q] = fmaf(S[4 * q], dA, dtx * bv.x);
-                    S[4 * q + 1] = fmaf(S[4 * q + 1], dA, dtx * bv.y);
-                    S[4 * q + 2] = fmaf(S[4 * q + 2], dA, dtx * bv.z);
-                    S[4 * q + 3] = fmaf(S[4 * q + 3], dA, dtx * bv.w);
+                    const uint64_t b01 = pair_f32(bv.x, bv.y), b23 = pair_f32(bv.z, bv.w);
+#pragma unroll
+                    for (int k = 0; k < PP; ++k) {
+                        S2[k][2 * q] = fma_pair(S2[k][2 * q], dA2, mul_pair(dtx2[k], b01));
+                        S2[k][2 * q + 1] = fma_pair(S2[k][2 * q + 1], dA2, mul_pair(dtx2[k], b23));
+                    }
                     if (MODE == 1) {
                         const float4 cv = Cj[L * q];
-                        acc = fmaf(S[4 * q], cv.x, acc);
-                        acc = fmaf(S[4 * q + 1], cv.y, acc);
-                        acc = fmaf(S[4 * q + 2], cv.z, acc);
-                        acc = fmaf(S[4 * q + 3], cv.w, acc);
+                        const uint64_t c01 = pair_f32(cv.x, cv.y), c23 = pair_f32(cv.z, cv.w);
+#pragma unroll
+                        for (int k = 0; k < PP; ++k) {
+                            acc_lo[k] = fma_pair(S2[k][2 * q], c01, acc_lo[k]);
+                            acc_hi[k] = fma_pair(S2[k][2 * q + 1], c23, acc_hi[k]);
+                        }
                     }
                 }
             }
             if (MODE == 1) {
-                for (int o = L >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-                if (l == 0 && active) a.y[(size_t)(row0 + j0 + j) * inner + h * P + p] = fmaf(Dh, xv, acc);
+#pragma unroll
+                for (int k = 0; k < PP; ++k) {
+                    float a0, a1, a2, a3;
+                    unpair_f32(acc_lo[k], a0, a1);
+                    unpair_f32(acc_hi[k], a2, a3);
+                    float acc = (a0 + a1) + (a2 + a3);
+#pragma unroll
+                    for (int o = L >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+                    if (l == 0 && mine) ys[j * PT + pl + k * PG] = fmaf(Dh, xs[j * PT + pl + k * PG], acc);
+                }
             } else {
                 decay *= dA;
+            }
+        }
+        if (MODE == 1) {
+            __syncthreads();
+            for (int i = tid; i < nb * PT; i += blockDim.x) {
+                const int j = i / PT, k = i % PT;
+                if (p0 + k < P) a.y[(size_t)(row0 + j0 + j) * inner + h * P + p0 + k] = ys[i];
             }
         }
     }
     float* dst = nullptr;
     if (MODE == 0) {
-        dst = a.scratch + (size_t)(base + c) * a.heads * P * N + hp;
+        dst = a.scratch + (size_t)(base + c) * a.heads * P * N + head_at;
         if (tid == 0 && blockIdx.z == 0) a.chunk_decay[(size_t)(base + c) * a.heads + h] = decay;
     } else if (c == n - 1) {
-        dst = a.state + slot * a.slot_stride + hp;
+        dst = a.state + slot * a.slot_stride + head_at;
     }
-    if (dst != nullptr) {
+    if (dst != nullptr && mine) {
 #pragma unroll
-        for (int q = 0; q < NPT / 4; ++q) {
-            if (!has[q]) continue;
-            const int n0 = 4 * (l + L * q);
-            if (vec) {
-                *reinterpret_cast<float4*>(dst + n0) = make_float4(S[4 * q], S[4 * q + 1], S[4 * q + 2], S[4 * q + 3]);
-            } else {
+        for (int k = 0; k < PP; ++k) {
+            const int p = p0 + pl + k * PG;
+            if (p >= P) continue;
 #pragma unroll
-                for (int k = 0; k < 4; ++k)
-                    if (n0 + k < N) dst[n0 + k] = S[4 * q + k];
+            for (int q = 0; q < NPT / 4; ++q) {
+                const int n0 = 4 * (l + L * q);
+                if (q >= nq || n0 >= N) continue;
+                float* at = dst + (size_t)p * N + n0;
+                float4 v;
+                unpair_f32(S2[k][2 * q], v.x, v.y);
+                unpair_f32(S2[k][2 * q + 1], v.z, v.w);
+                if (vec) *reinterpret_cast<float4*>(at) = v;
+                else {
+                    at[0] = v.x;
+                    if (n0 + 1 < N) at[1] = v.y;
+                    if (n0 + 2 < N) at[2] = v.z;
+                    if (n0 + 3 < N) at[3] = v.w;
+                }
             }
         }
     }
@@ -292,29 +380,46 @@ VCB_API int vcb_ssm_scan(const float* u, int S, long long s_stride, long long ld
     VCB_CHECK_ARG(P >= 1 && Q >= NB && Q % NB == 0, "ssm_scan: bad sizes P=%d Q=%d", P, Q);
     VCB_CHECK_ARG(!multi || (scratch != nullptr && chunk_decay != nullptr), "ssm_scan: chunks need their scratch");
     VCB_CHECK_ARG(n_chunks <= 0x7fffffff / 1 && heads <= 65535 && E <= 65535, "ssm_scan: too many heads or entries");
+    const int N4 = (N + 3) / 4;
     int L = 1;
-    while (L * NPT < 4 * ((N + 3) / 4)) L <<= 1;
-    const int npt = NPT;
-    int PT = 256 / L;
-    if (PT < 1) PT = 1;
-    if (PT > P) PT = P;
-    const int threads = (PT * L + 31) / 32 * 32;
+    while (L * (NPT / 4) < N4) L <<= 1;
+    const int nq = (N4 + L - 1) / L;          // 16-byte pieces of the state a thread holds
+    int PG = 256 / L;                          // threads side by side, each with PP value lanes
+    if (PG > 32) PG = 32;
+    if (PG * PP > P) PG = (P + PP - 1) / PP;
+    const int PT = PG * PP;                    // value lanes per block
+    const int threads = (PG * L + 31) / 32 * 32;
     const int ptiles = (P + PT - 1) / PT;
     VCB_CHECK_ARG(ptiles <= 65535, "ssm_scan: too many tiles of value lanes");
     SsmArgs args{Rows{u, S < 1 ? 1 : S, s_stride, ld}, dt_col, xbc, ldx, dt_bias, a_rate, D, state, slot_stride, q_start, q_len,
-                 slots, E, heads, P, N, groups, Q, scratch, chunk_decay, y, L, npt, PT};
-    const size_t smem = ((size_t)2 * NB * 4 * ((N + 3) / 4) + (size_t)NB * PT + 2 * NB) * sizeof(float);
+                 slots, E, heads, P, N, groups, Q, scratch, chunk_decay, y, L, nq, PT};
+    const size_t smem = ((size_t)2 * NB * 4 * nq * L + (size_t)3 * NB * PT + NB) * sizeof(float);
+    VCB_CHECK_ARG(smem <= 48 * 1024, "ssm_scan: %d state lanes need more shared memory than a block has by default", N);
     const dim3 grid(n_chunks, heads, ptiles);
     const bool f32 = xbc_dtype == VCB_F32;
+#define VCB_SSM(MODE, LL)                                                                                              \
+    do {                                                                                                               \
+        if (f32) launch_pdl(ssm_scan_kernel<float, MODE, LL>, grid, dim3(threads), smem, stream, args);                \
+        else launch_pdl(ssm_scan_kernel<__nv_bfloat16, MODE, LL>, grid, dim3(threads), smem, stream, args);            \
+    } while (0)
+#define VCB_SSM_L(MODE)                                                                                                \
+    switch (L) {                                                                                                       \
+        case 1: VCB_SSM(MODE, 1); break;                                                                               \
+        case 2: VCB_SSM(MODE, 2); break;                                                                               \
+        case 4: VCB_SSM(MODE, 4); break;                                                                               \
+        case 8: VCB_SSM(MODE, 8); break;                                                                               \
+        case 16: VCB_SSM(MODE, 16); break;                                                                             \
+        default: VCB_SSM(MODE, 32); break;                                                                             \
+    }
     if (multi) {
-        if (f32) launch_pdl(ssm_scan_kernel<float, 0>, grid, dim3(threads), smem, stream, args);
-        else launch_pdl(ssm_scan_kernel<__nv_bfloat16, 0>, grid, dim3(threads), smem, stream, args);
+        VCB_SSM_L(0)
         VCB_CHECK_LAUNCH("ssm_chunk_state");
         launch_pdl(ssm_chunk_carry_kernel, dim3(E, heads, (unsigned)(((size_t)P * N + 255) / 256)), dim3(256), 0, stream, args);
         VCB_CHECK_LAUNCH("ssm_chunk_carry");
     }
-    if (f32) launch_pdl(ssm_scan_kernel<float, 1>, grid, dim3(threads), smem, stream, args);
-    else launch_pdl(ssm_scan_kernel<__nv_bfloat16, 1>, grid, dim3(threads), smem, stream, args);
+    VCB_SSM_L(1)
+#undef VCB_SSM_L
+#undef VCB_SSM
     VCB_CHECK_LAUNCH("ssm_scan");
     return 0;
 }
