@@ -459,6 +459,8 @@ def run_attention(dtype, nh, nkv, d, dv, ps, shapes, cap, slope_exponent=8.0, si
     q_flat = torch.cat(qs).to(dtype).to(dev()).view(T, nh * d)
     args = (pages, bt.to(dev()), i32(ctx.host_q_start), i32(ctx.host_q_len), i32(ctx.host_ctx_len))
     opts = dict(scale=scale, softcap=cap or 0.0, slope=slopes.float().to(dev()), sink=sink)
+    wants = [[P.attend_head(q[:, h], k[:, h // (nh // nkv)], v[:, h // (nh // nkv)], scale, cap, float(slopes[h]) if slope_exponent else 0.0)
+              for h in range(nh)] for q, (k, v) in zip(qs, seqs)]
     plans = {}
     for kernel in kernels:
         mma = kernel != "plain"
@@ -488,10 +490,9 @@ def run_attention(dtype, nh, nkv, d, dv, ps, shapes, cap, slope_exponent=8.0, si
         got = out.double().cpu().view(T, nh, dv)
         tol = dict(atol=2e-5, rtol=2e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
         t = 0
-        for (start, n), q, (k, v) in zip(shapes, qs, seqs):
+        for (start, n), want in zip(shapes, wants):
             for h in range(nh):
-                want = P.attend_head(q[:, h], k[:, h // (nh // nkv)], v[:, h // (nh // nkv)], scale, cap, float(slopes[h]) if slope_exponent else 0.0)
-                torch.testing.assert_close(got[t:t + n, h], want, **tol, msg=lambda m: f"{kernel}, entry at {start}+{n}, head {h}: {m}")
+                torch.testing.assert_close(got[t:t + n, h], want[h], **tol, msg=lambda m: f"{kernel}, entry at {start}+{n}, head {h}: {m}")
             t += n
     return plans
 
@@ -519,7 +520,9 @@ MIXED_SHAPES = [(0, 1), (0, 37), (300, 1), (5, 2), (63, 1), (64, 1), (17, 130), 
 def test_capped_sloped_sink_attention_mixed_batch(dtype, nh, nkv, d, dv, ps, cap):
     """First tokens of a sequence, single tokens behind short and long contexts (sliced key ranges that are merged, the
     sink counted once), portions that start inside a page and span many tiles; one head (slope 2^-8) to forty."""
-    plans = run_attention(dtype, nh, nkv, d, dv, ps, MIXED_SHAPES, cap, kernels=attention_kernels(dtype, d, dv, ps))
+    # (forty heads on the plain implementation: the shorter contexts are enough to see every one of them)
+    shapes = MIXED_SHAPES if nh <= 8 else [s for s in MIXED_SHAPES if s[0] + s[1] <= 200] + [(1100, 1)]
+    plans = run_attention(dtype, nh, nkv, d, dv, ps, shapes, cap, kernels=attention_kernels(dtype, d, dv, ps))
     assert plans["plain"].nslices > 1
 
 
