@@ -264,6 +264,35 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __res
     out[(size_t)t * W + c] = v;
 }
 
+// four channels a thread (W a multiple of 4, every base and stride a multiple of 4 elements)
+__global__ void moe_combine_vec_kernel(const float* __restrict__ y, const int* __restrict__ pos_of, const float* __restrict__ sel_w,
+                                       int top, Rows shared, const int* __restrict__ q_start, const int* __restrict__ q_len,
+                                       int n_entries, int W, float* __restrict__ out) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.y;
+    const int c = 4 * (blockIdx.x * blockDim.x + threadIdx.x);
+    if (c >= W || entry_of_row(q_start, q_len, n_entries, t) < 0) return;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (shared.p != nullptr) {
+        const float* p = shared.p + (long long)t * shared.ld + c;
+        for (int s = 0; s < shared.S; ++s) {
+            const float4 a = *reinterpret_cast<const float4*>(p + (long long)s * shared.s_stride);
+            v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+        }
+    }
+    for (int k = 0; k < top; ++k) {
+        const int pos = pos_of[(size_t)t * top + k];
+        if (pos >= 0) {
+            const float4 r = *reinterpret_cast<const float4*>(y + (size_t)pos * W + c);
+            const float wt = sel_w != nullptr ? sel_w[(size_t)t * top + k] : 1.f;
+            if (sel_w != nullptr) { v.x += r.x * wt; v.y += r.y * wt; v.z += r.z * wt; v.w += r.w * wt; }
+            else { v.x += r.x; v.y += r.y; v.z += r.z; v.w += r.w; }
+        }
+    }
+    *reinterpret_cast<float4*>(out + (size_t)t * W + c) = v;
+}
+
 }  // namespace
 
 VCB_API int vcb_moe_tile_rows() { return BM; }
@@ -341,6 +370,13 @@ VCB_API int vcb_moe_combine(const float* y, const int* pos_of, const float* sel_
                             float* out, cudaStream_t stream) {
     if (T == 0) return 0;
     VCB_CHECK_ARG(T <= 65535, "moe_combine: %d rows in one step (at most 65535)", T);
+    if (W % 4 == 0 && (uintptr_t)y % 16 == 0 && (uintptr_t)out % 16 == 0 &&
+        (shared == nullptr || ((uintptr_t)shared % 16 == 0 && ld % 4 == 0 && (S <= 1 || s_stride % 4 == 0)))) {
+        launch_pdl(moe_combine_vec_kernel, dim3((W / 4 + 127) / 128, T), dim3(128), 0, stream, y, pos_of, sel_w, top,
+                   Rows{shared, S < 1 ? 1 : S, s_stride, ld}, q_start, q_len, n_entries, W, out);
+        VCB_CHECK_LAUNCH("moe_combine");
+        return 0;
+    }
     launch_pdl(moe_combine_kernel, dim3((W + 255) / 256, T), dim3(256), 0, stream, y, pos_of, sel_w, top,
                Rows{shared, S < 1 ? 1 : S, s_stride, ld}, q_start, q_len, n_entries, W, out);
     VCB_CHECK_LAUNCH("moe_combine");

@@ -45,6 +45,34 @@ __device__ __forceinline__ float rows_at(const Rows& in, long long t, int c) {
     return v;
 }
 
+// four neighbouring channels at once (c a multiple of 4, every stride and base a multiple of 4 elements)
+__device__ __forceinline__ float4 rows_at4(const Rows& in, long long t, int c) {
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float* p = in.p + t * in.ld + c;
+    for (int s = 0; s < in.S; ++s) {
+        const float4 a = *reinterpret_cast<const float4*>(p + (long long)s * in.s_stride);
+        v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+    }
+    if (in.bias != nullptr) {
+        const float4 b = *reinterpret_cast<const float4*>(in.bias + c);
+        v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+    }
+    return v;
+}
+inline bool rows_vec_ok(const Rows& r) {
+    return r.p == nullptr || (((uintptr_t)r.p % 16 == 0) && r.ld % 4 == 0 && (r.S <= 1 || r.s_stride % 4 == 0) &&
+                              (r.bias == nullptr || (uintptr_t)r.bias % 16 == 0));
+}
+template <typename T> __device__ __forceinline__ void store4(T* p, float4 v);
+template <> __device__ __forceinline__ void store4<float>(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* p, float4 v) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 u;
+    u.x = *reinterpret_cast<const uint32_t*>(&a);
+    u.y = *reinterpret_cast<const uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(p) = u;
+}
+
 __device__ __forceinline__ float act_of(float x, int kind) {
     switch (kind) {
         case 0: return 0.5f * x * (1.f + erff(x * 0.70710678118654752440f));
@@ -115,6 +143,70 @@ __global__ void postnorm_add_norm_kernel(float* __restrict__ resid, Rows y, cons
     const float mul2 = 1.f / sqrtf(s2 / (float)H + eps_n);
     for (int c = threadIdx.x; c < H; c += blockDim.x)
         out[(size_t)i * H + c] = from_f32<TOUT>(vals[c] * mul2 * wn[c]);
+}
+
+// the same with four channels a thread and the row held in registers: every load of the row is asked for before the
+// first result is needed
+template <typename TOUT, int VPT>
+__global__ __launch_bounds__(1024) void postnorm_add_norm_vec_kernel(float* __restrict__ resid, Rows y, const float* __restrict__ wb,
+                                                                     const float* __restrict__ ls, float eps_b,
+                                                                     const int* __restrict__ q_start, const int* __restrict__ q_len,
+                                                                     int E, int H, const float* __restrict__ wn, float eps_n,
+                                                                     TOUT* __restrict__ out, const int* __restrict__ rows) {
+    __shared__ float scratch[33];
+    pdl_trigger();
+    pdl_wait();
+    const int i = blockIdx.x;
+    const long long t = rows != nullptr ? rows[i] : i;
+    if (rows == nullptr && entry_of_row(q_start, q_len, E, (int)t) < 0) return;
+    const int nv = H >> 2;
+    float4 v[VPT], r[VPT];
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+        const int idx = threadIdx.x + k * blockDim.x;
+        if (idx < nv) {
+            r[k] = *reinterpret_cast<const float4*>(resid + (size_t)t * H + 4 * idx);
+            if (y.p != nullptr) v[k] = rows_at4(y, t, 4 * idx);
+        }
+    }
+    float mul = 0.f;
+    if (y.p != nullptr) {
+        float ss = 0.f;
+#pragma unroll
+        for (int k = 0; k < VPT; ++k)
+            if (threadIdx.x + k * blockDim.x < nv) ss += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+        ss = block_sum(ss, scratch);
+        mul = 1.f / sqrtf(ss / (float)H + eps_b);
+    }
+    float s2 = 0.f;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+        const int idx = threadIdx.x + k * blockDim.x;
+        if (idx < nv) {
+            if (y.p != nullptr) {
+                float4 d = *reinterpret_cast<const float4*>(wb + 4 * idx);
+                d.x *= v[k].x * mul; d.y *= v[k].y * mul; d.z *= v[k].z * mul; d.w *= v[k].w * mul;
+                if (ls != nullptr) {
+                    const float4 l = *reinterpret_cast<const float4*>(ls + 4 * idx);
+                    d.x *= l.x; d.y *= l.y; d.z *= l.z; d.w *= l.w;
+                }
+                r[k].x += d.x; r[k].y += d.y; r[k].z += d.z; r[k].w += d.w;
+                if (rows == nullptr) *reinterpret_cast<float4*>(resid + (size_t)t * H + 4 * idx) = r[k];
+            }
+            s2 += r[k].x * r[k].x + r[k].y * r[k].y + r[k].z * r[k].z + r[k].w * r[k].w;
+        }
+    }
+    if (out == nullptr) return;
+    s2 = block_sum(s2, scratch);
+    const float mul2 = 1.f / sqrtf(s2 / (float)H + eps_n);
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+        const int idx = threadIdx.x + k * blockDim.x;
+        if (idx < nv) {
+            const float4 g = *reinterpret_cast<const float4*>(wn + 4 * idx);
+            store4<TOUT>(out + (size_t)i * H + 4 * idx, make_float4(r[k].x * mul2 * g.x, r[k].y * mul2 * g.y, r[k].z * mul2 * g.z, r[k].w * mul2 * g.w));
+        }
+    }
 }
 
 struct QkvWholeArgs {
@@ -234,6 +326,18 @@ VCB_API int vcb_postnorm_add_norm(float* resid, const float* y, int Sy, long lon
     VCB_CHECK_ARG(y == nullptr || wb != nullptr, "postnorm_add_norm: a result to add needs the gain of its norm");
     VCB_CHECK_ARG((out == nullptr) == (wn == nullptr), "postnorm_add_norm: the next norm needs both its gain and its output");
     Rows ry{y, Sy < 1 ? 1 : Sy, y_stride, ldy, yb};
+    if (H % 4 == 0 && H / 4 <= 4096 && rows_vec_ok(ry) && (uintptr_t)resid % 16 == 0 && (uintptr_t)wb % 16 == 0 && (uintptr_t)ls % 16 == 0 &&
+        (uintptr_t)wn % 16 == 0 && (uintptr_t)out % 16 == 0) {
+        const int nv = H / 4;
+        const int vpt = nv <= 512 ? 1 : (nv <= 2048 ? 2 : 4);     // (two blocks of 512 threads fit an SM)
+        const int threads4 = ((nv + vpt - 1) / vpt + 31) / 32 * 32;
+#define VCB_PNA(TOUT, V) launch_pdl(postnorm_add_norm_vec_kernel<TOUT, V>, dim3(n), dim3(threads4), 0, stream, resid, ry, wb, ls, eps_b, q_start, q_len, E, H, wn, eps_n, (TOUT*)out, rows)
+        if (out_dtype == VCB_F32) { if (vpt == 1) VCB_PNA(float, 1); else if (vpt == 2) VCB_PNA(float, 2); else VCB_PNA(float, 4); }
+        else { if (vpt == 1) VCB_PNA(__nv_bfloat16, 1); else if (vpt == 2) VCB_PNA(__nv_bfloat16, 2); else VCB_PNA(__nv_bfloat16, 4); }
+#undef VCB_PNA
+        VCB_CHECK_LAUNCH("postnorm_add_norm");
+        return 0;
+    }
     const size_t smem = ((size_t)H + 64) * sizeof(float);
     const int threads = H >= 4096 ? 1024 : (H >= 1024 ? 512 : 256);
     if (out_dtype == VCB_F32) {

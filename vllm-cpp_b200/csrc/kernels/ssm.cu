@@ -363,6 +363,70 @@ __global__ void gated_group_norm_kernel(const float* __restrict__ y, Rows z, con
         out[(size_t)t * C + c0 + k] = from_f32<TOUT>(vals[k] * mul * w[c0 + k]);
 }
 
+// the same with four channels a thread, the part's values held in registers
+template <typename TOUT, int VPT>
+__global__ __launch_bounds__(1024) void gated_group_norm_vec_kernel(const float* __restrict__ y, Rows z, const float* __restrict__ w,
+                                                                    float eps, const int* __restrict__ q_start,
+                                                                    const int* __restrict__ q_len, int E, int C, int gs,
+                                                                    TOUT* __restrict__ out) {
+    __shared__ float scratch[33];
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x, c0 = blockIdx.y * gs;
+    if (entry_of_row(q_start, q_len, E, t) < 0) return;
+    const int nv = gs >> 2;
+    float4 v[VPT];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+        const int idx = threadIdx.x + k * blockDim.x;
+        if (idx < nv) {
+            const int c = c0 + 4 * idx;
+            float4 zz = make_float4(0.f, 0.f, 0.f, 0.f);
+            const float* zp = z.p + (long long)t * z.ld + c;
+            for (int s = 0; s < z.S; ++s) {
+                const float4 a = *reinterpret_cast<const float4*>(zp + (long long)s * z.s_stride);
+                zz.x += a.x; zz.y += a.y; zz.z += a.z; zz.w += a.w;
+            }
+            const float4 yy = *reinterpret_cast<const float4*>(y + (size_t)t * C + c);
+            v[k] = make_float4(yy.x * (zz.x / (1.f + expf(-zz.x))), yy.y * (zz.y / (1.f + expf(-zz.y))),
+                               yy.z * (zz.z / (1.f + expf(-zz.z))), yy.w * (zz.w / (1.f + expf(-zz.w))));
+            ss += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+        }
+    }
+    ss = block_sum(ss, scratch);
+    const float mul = 1.f / sqrtf(ss / (float)gs + eps);
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+        const int idx = threadIdx.x + k * blockDim.x;
+        if (idx < nv) {
+            const int c = c0 + 4 * idx;
+            const float4 g = *reinterpret_cast<const float4*>(w + c);
+            const float4 o = make_float4(v[k].x * mul * g.x, v[k].y * mul * g.y, v[k].z * mul * g.z, v[k].w * mul * g.w);
+            if (sizeof(TOUT) == 4) *reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + (size_t)t * C + c) = o;
+            else {
+                const __nv_bfloat162 a = __floats2bfloat162_rn(o.x, o.y), b = __floats2bfloat162_rn(o.z, o.w);
+                uint2 u;
+                u.x = *reinterpret_cast<const uint32_t*>(&a);
+                u.y = *reinterpret_cast<const uint32_t*>(&b);
+                *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(out) + (size_t)t * C + c) = u;
+            }
+        }
+    }
+}
+
+// a launch of one build of the scan kernel; shared memory beyond the default 48 KB has to be asked for per build (all
+// builds have one function type, so nothing is remembered here: the call is a few microseconds of host time)
+template <typename K>
+int scan_launch(K kern, dim3 grid, int threads, size_t smem, cudaStream_t stream, const SsmArgs& args) {
+    if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+        vcb_set_error("ssm_scan: %zu bytes of shared memory refused", smem);
+        return -2;
+    }
+    launch_pdl(kern, grid, dim3(threads), smem, stream, args);
+    return 0;
+}
+
 }  // namespace
 
 // The three kernels of the recurrence.  u: the input projection's sums [S][T][ld] (dt of head h in column dt_col + h);
@@ -394,13 +458,13 @@ VCB_API int vcb_ssm_scan(const float* u, int S, long long s_stride, long long ld
     SsmArgs args{Rows{u, S < 1 ? 1 : S, s_stride, ld}, dt_col, xbc, ldx, dt_bias, a_rate, D, state, slot_stride, q_start, q_len,
                  slots, E, heads, P, N, groups, Q, scratch, chunk_decay, y, L, nq, PT};
     const size_t smem = ((size_t)2 * NB * 4 * nq * L + (size_t)3 * NB * PT + NB) * sizeof(float);
-    VCB_CHECK_ARG(smem <= 48 * 1024, "ssm_scan: %d state lanes need more shared memory than a block has by default", N);
+    VCB_CHECK_ARG(smem <= 200 * 1024, "ssm_scan: %d state lanes need more shared memory than a block has", N);
     const dim3 grid(n_chunks, heads, ptiles);
     const bool f32 = xbc_dtype == VCB_F32;
 #define VCB_SSM(MODE, LL)                                                                                              \
     do {                                                                                                               \
-        if (f32) launch_pdl(ssm_scan_kernel<float, MODE, LL>, grid, dim3(threads), smem, stream, args);                \
-        else launch_pdl(ssm_scan_kernel<__nv_bfloat16, MODE, LL>, grid, dim3(threads), smem, stream, args);            \
+        if (f32) { if (int rc = scan_launch(ssm_scan_kernel<float, MODE, LL>, grid, threads, smem, stream, args)) return rc; }            \
+        else { if (int rc = scan_launch(ssm_scan_kernel<__nv_bfloat16, MODE, LL>, grid, threads, smem, stream, args)) return rc; }       \
     } while (0)
 #define VCB_SSM_L(MODE)                                                                                                \
     switch (L) {                                                                                                       \
@@ -432,6 +496,18 @@ VCB_API int vcb_gated_group_norm(const float* y, const float* z, int S, long lon
     VCB_CHECK_ARG(parts >= 1 && C % parts == 0 && parts <= 65535, "gated_group_norm: %d channels in %d parts", C, parts);
     const int gs = C / parts;
     Rows rz{z, S < 1 ? 1 : S, s_stride, ld};
+    if (gs % 4 == 0 && gs / 4 <= 4096 && (uintptr_t)y % 16 == 0 && (uintptr_t)z % 16 == 0 && ld % 4 == 0 && (S <= 1 || s_stride % 4 == 0) &&
+        (uintptr_t)w % 16 == 0 && (uintptr_t)out % 16 == 0 && C % 4 == 0) {
+        const int nv = gs / 4;
+        const int vpt = nv <= 256 ? 1 : (nv <= 2048 ? 2 : 4);
+        const int threads4 = ((nv + vpt - 1) / vpt + 31) / 32 * 32;
+#define VCB_GGN(TOUT, V) launch_pdl(gated_group_norm_vec_kernel<TOUT, V>, dim3(T, parts), dim3(threads4), 0, stream, y, rz, w, eps, q_start, q_len, E, C, gs, (TOUT*)out)
+        if (out_dtype == VCB_F32) { if (vpt == 1) VCB_GGN(float, 1); else if (vpt == 2) VCB_GGN(float, 2); else VCB_GGN(float, 4); }
+        else { if (vpt == 1) VCB_GGN(__nv_bfloat16, 1); else if (vpt == 2) VCB_GGN(__nv_bfloat16, 2); else VCB_GGN(__nv_bfloat16, 4); }
+#undef VCB_GGN
+        VCB_CHECK_LAUNCH("gated_group_norm");
+        return 0;
+    }
     const size_t smem = ((size_t)gs + 64) * sizeof(float);
     VCB_CHECK_ARG(smem <= 200 * 1024, "gated_group_norm: parts of %d channels are too long", gs);
     const int threads = gs >= 2048 ? 1024 : (gs >= 512 ? 512 : 256);
