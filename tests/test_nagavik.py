@@ -607,11 +607,12 @@ def run_recurrence(heads, Pv, N, groups, steps, dtype, S, rates, n_slots=3):
 
 @gpu
 @pytest.mark.parametrize("dtype,S", [(torch.float32, 1), (torch.bfloat16, 3)])
-@pytest.mark.parametrize("heads,Pv,N,groups", [(4, 8, 16, 2), (3, 5, 7, 1), (2, 64, 128, 2), (5, 6, 33, 5), (1, 20, 200, 1), (2, 40, 56, 1), (1, 300, 4, 1)])
+@pytest.mark.parametrize("heads,Pv,N,groups", [(4, 8, 16, 2), (3, 5, 7, 1), (2, 64, 128, 2), (5, 6, 33, 5), (1, 20, 200, 1), (2, 40, 56, 1), (1, 300, 4, 1), (1, 8, 300, 1)])
 def test_recurrence_in_portions_equals_the_whole(dtype, S, heads, Pv, N, groups):
     """Portions of one token, of two, of a chunk and one more, of several chunks, beside a request of other lengths; decay
     rates from 0.002 (the first tokens still count after hundreds) to 3 (the state is gone in two); the state in its slot
-    between the steps."""
+    between the steps.  Shapes: state lanes that are no multiple of four, one state lane run per thread and four, more
+    value lanes than a block takes, 300 state lanes (more shared memory than a block has by default)."""
     steps = [(3, 1), (1, 1), (2, 33), (1, 2), (70, 1), (32, 64), (1, 97), (2, 2), (129, 1)]
     rates = torch.logspace(math.log10(0.002), math.log10(3.0), heads).tolist()
     got, state, want = run_recurrence(heads, Pv, N, groups, steps, dtype, S, rates)
