@@ -414,6 +414,18 @@ def test_convolution_with_bias_and_silu_in_portions_equals_the_whole(taps, C, S,
         torch.testing.assert_close(a, b, **tol)
 
 
+@gpu
+@pytest.mark.parametrize("taps,C,S,dtype", [(4, 96, 1, torch.bfloat16), (1, 8, 2, torch.float32), (8, 300, 1, torch.float32), (3, 20, 3, torch.float32)])
+def test_convolution_of_long_steps(taps, C, S, dtype):
+    """Steps of more than 512 rows (the kernel that walks runs of rows with the taps' inputs in registers): entries that
+    start and end inside a run, a run that begins in the middle of an entry, single tokens between long portions."""
+    steps = [(530, 1), (1, 1), (300, 411), (2, 2), (1, 700), (17, 1)]
+    got, want = conv_in_steps(C, taps, steps, dtype, S)
+    tol = dict(atol=3e-5, rtol=3e-5) if dtype == torch.float32 else dict(atol=3e-2, rtol=2e-2)
+    for a, b in zip(got, want):
+        torch.testing.assert_close(a, b, **tol)
+
+
 def run_attention(dtype, nh, nkv, d, dv, ps, shapes, cap, slope_exponent=8.0, sink=True, craft=None, scale=0.3, kernels=("plain",)):
     """shapes: [(tokens cached before the step, query tokens of the step)]; compares the attention kernels (decoded tokens
     with sliced key ranges, prompt portions in query tiles) with the plain attention of one head at a time."""

@@ -210,6 +210,77 @@ __global__ void causal_conv_vec_kernel(RowsIn in, const float* __restrict__ w, f
     if (taps > 1 && q_len[e] == 1) state_push4(state + (long long)slots[e] * slot_stride, C, taps, c, u);
 }
 
+// The same for steps of many rows: a thread walks a run of RUN rows for its four channels and keeps the window of the last
+// inputs in registers, so every input row is fetched once (not once per tap) and the entry is looked up once per run (or
+// where a row leaves it).  The window and the taps are held right-aligned in MAX_TAPS places, the unused older ones zero:
+// the sum runs over them from the oldest to the newest, which is the order conv_at4 adds in.
+template <typename TOUT, int RUN>
+__global__ __launch_bounds__(128) void causal_conv_run_kernel(RowsIn in, const float* __restrict__ w, float* __restrict__ state,
+                                                              long long slot_stride, const int* __restrict__ q_start,
+                                                              const int* __restrict__ q_len, const int* __restrict__ slots, int E, int T,
+                                                              int C, int taps, int add_input, TOUT* __restrict__ out_conv,
+                                                              TOUT* __restrict__ out_copy, const float* __restrict__ out_bias, int act) {
+    pdl_trigger();
+    pdl_wait();
+    const int c = 4 * (blockIdx.x * blockDim.x + threadIdx.x);
+    if (c >= C) return;
+    const int t0 = blockIdx.y * RUN, t1 = min(T, t0 + RUN);
+    float wr[4][MAX_TAPS];
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+#pragma unroll
+        for (int b = 0; b < MAX_TAPS; ++b) wr[k][MAX_TAPS - 1 - b] = b < taps ? w[(long long)(c + k) * taps + (taps - 1 - b)] : 0.f;
+    float4 ob = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (out_bias != nullptr) ob = *reinterpret_cast<const float4*>(out_bias + c);
+    float4 win[MAX_TAPS];      // win[MAX_TAPS - 1 - b]: the input b rows back
+#pragma unroll
+    for (int i = 0; i < MAX_TAPS; ++i) win[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    int e = -1, e_start = 0, e_end = 0, e_len = 0;
+    float* st = nullptr;
+    for (int t = t0; t < t1; ++t) {
+        if (e < 0 || t >= e_end) {
+            e = entry_of_row(q_start, q_len, E, t);
+            if (e < 0) continue;
+            e_start = q_start[e];
+            e_len = q_len[e];
+            e_end = e_start + e_len;
+            st = taps > 1 ? state + (long long)slots[e] * slot_stride : nullptr;
+            const int rel = t - e_start;
+#pragma unroll
+            for (int b = 1; b < MAX_TAPS; ++b) {
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (b < taps) v = rel - b >= 0 ? rows_at4(in, t - b, c) : *reinterpret_cast<const float4*>(st + (long long)(rel - b + taps - 1) * C + c);
+                win[MAX_TAPS - 1 - b] = v;
+            }
+        }
+        const float4 u = rows_at4(in, t, c);
+        win[MAX_TAPS - 1] = u;
+        if (out_copy != nullptr) store4<TOUT>(out_copy + (size_t)t * C + c, u);
+        if (out_conv != nullptr) {
+            float4 y = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (taps > 0) {
+#pragma unroll
+                for (int i = 0; i < MAX_TAPS; ++i) {
+                    y.x = fmaf(wr[0][i], win[i].x, y.x);
+                    y.y = fmaf(wr[1][i], win[i].y, y.y);
+                    y.z = fmaf(wr[2][i], win[i].z, y.z);
+                    y.w = fmaf(wr[3][i], win[i].w, y.w);
+                }
+            }
+            if (add_input) { y.x += u.x; y.y += u.y; y.z += u.z; y.w += u.w; }
+            if (out_bias != nullptr) { y.x += ob.x; y.y += ob.y; y.z += ob.z; y.w += ob.w; }
+            if (act == 1) {
+                y.x = y.x / (1.f + expf(-y.x)); y.y = y.y / (1.f + expf(-y.y));
+                y.z = y.z / (1.f + expf(-y.z)); y.w = y.w / (1.f + expf(-y.w));
+            }
+            store4<TOUT>(out_conv + (size_t)t * C + c, y);
+        }
+        if (taps > 1 && e_len == 1) state_push4(st, C, taps, c, u);
+#pragma unroll
+        for (int i = 0; i < MAX_TAPS - 1; ++i) win[i] = win[i + 1];
+    }
+}
+
 __global__ void conv_state_update_kernel(RowsIn in, float* __restrict__ state, long long slot_stride,
                                          const int* __restrict__ q_start, const int* __restrict__ q_len,
                                          const int* __restrict__ slots, int C, int taps) {
@@ -518,6 +589,19 @@ VCB_API int vcb_causal_conv(const float* in, int S, long long s_stride, long lon
     const bool vec = C % 4 == 0 && rows_vec_ok(r) && (uintptr_t)out_conv % 16 == 0 && (uintptr_t)out_copy % 16 == 0 &&
                      (uintptr_t)out_bias % 16 == 0 &&
                      (state == nullptr || ((uintptr_t)state % 16 == 0 && slot_stride % 4 == 0));
+    if (vec && T >= 512) {
+        // many rows: runs of 16 rows a thread, the inputs fetched once
+        constexpr int RUN = 16;
+        const dim3 gridr((C / 4 + 127) / 128, (T + RUN - 1) / RUN), blockr(128);
+        if (out_dtype == VCB_F32)
+            launch_pdl(causal_conv_run_kernel<float, RUN>, gridr, blockr, 0, stream, r, w, state, slot_stride, q_start, q_len, slots, E, T,
+                       C, taps, add_input, (float*)out_conv, (float*)out_copy, out_bias, act);
+        else
+            launch_pdl(causal_conv_run_kernel<__nv_bfloat16, RUN>, gridr, blockr, 0, stream, r, w, state, slot_stride, q_start, q_len,
+                       slots, E, T, C, taps, add_input, (__nv_bfloat16*)out_conv, (__nv_bfloat16*)out_copy, out_bias, act);
+        VCB_CHECK_LAUNCH("causal_conv");
+        return 0;
+    }
     if (vec) {
         const dim3 grid4((C / 4 + 127) / 128, T), block4(128);
         if (out_dtype == VCB_F32)
